@@ -1,0 +1,136 @@
+/* b200llama — C ABI of the B200 (sm_100a) decode engine for Llama-family models stored as
+ * GGUF Q8_0 / Q4_K / Q6_K blocks.
+ *
+ * The reference (tinyllama.cpp) has no FFI boundary for its forward pass; the closest seam is
+ * the C++ member-function surface of TinyLlamaModel / KVCache (model.h:324-399, model.h:153-230)
+ * and the raw-pointer op layer below it (cuda_kernels.h:104-643). Every entry point here names
+ * the reference interface it stands in for. All functions return 0 on success and a non-zero
+ * status otherwise; nothing throws across this boundary (the reference throws
+ * std::runtime_error from gpuErrchk, cuda_kernels.h:66-82, or returns an empty vector,
+ * model.cpp:828-839); the text of the last failure on the calling thread is available from
+ * b200_last_error(). Host pointers are plain memory owned by the caller. One engine is bound to
+ * one CUDA device and must be driven from one host thread at a time, like the reference's model.
+ */
+#ifndef B200LLAMA_H
+#define B200LLAMA_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml tensor types accepted (ggml_types.h:21-42) */
+enum { B200_TYPE_F32 = 0, B200_TYPE_Q8_0 = 8, B200_TYPE_Q4_K = 12, B200_TYPE_Q6_K = 14 };
+/* KV cache element types: FP32 (KVCacheLayer::k_dev_fp32, model.h:137-138) or INT8 with one FP32
+ * scale per (position, kv head) (k_dev_quantized / k_dev_scales, model.h:140-143). */
+enum { B200_KV_F32 = 0, B200_KV_I8 = 1 };
+
+typedef struct b200_engine b200_engine;
+
+/* Mirrors the fields of ModelConfig (model.h:80-120) the forward pass reads, plus engine options. */
+typedef struct b200_model_desc {
+  int32_t hidden_size;
+  int32_t intermediate_size;
+  int32_t num_attention_heads;
+  int32_t num_key_value_heads;
+  int32_t num_hidden_layers;
+  int32_t vocab_size;
+  int32_t max_position_embeddings; /* RoPE table length (gpu_initialization.cpp:48-58) */
+  float rms_norm_eps;
+  float rope_theta;
+  int32_t kv_dtype;   /* B200_KV_F32 | B200_KV_I8 (ModelConfig::use_kvcache_quantization) */
+  int32_t max_seqs;   /* KV slots = KVCache::max_batch_size (model.h:168) */
+  int32_t max_ctx;    /* positions held per slot; 0 = max_position_embeddings */
+  int32_t act_planes; /* integer byte-planes the activations are split into for the GEMV: 2 or 3 (0 = 3) */
+  int32_t device;     /* CUDA device ordinal */
+  int32_t tp_rank;    /* tensor-parallel rank and world size (1 = single GPU) */
+  int32_t tp_size;
+  uint8_t nccl_id[128]; /* ncclUniqueId shared by all ranks when tp_size > 1 (see b200_nccl_unique_id) */
+} b200_model_desc;
+
+const char* b200_last_error(void);
+int b200_device_count(int* count);
+
+/* ---- engine life cycle: replaces TinyLlamaModel(config, gguf_path) (model.cpp:154),
+ * map_gguf_weights (weight_management.cpp:677), initialize_gpu_and_rope
+ * (gpu_initialization.cpp:15) and KVCache::initialize (kv_cache.cpp:10). Linear weights stay in
+ * their packed block form on the device; nothing is expanded to FP32. ---- */
+int b200_engine_create(const b200_model_desc* desc, b200_engine** out);
+/* One GGUF tensor by its GGUF name ("blk.3.attn_q.weight", "token_embd.weight", ...). rows x cols
+ * with cols = the input dimension (GGUF ne0). host_data holds the tensor exactly as stored in the file. */
+int b200_engine_upload_tensor(b200_engine* e, const char* gguf_name, int ggml_type, const void* host_data,
+                              size_t bytes, int64_t rows, int64_t cols);
+/* Checks that every tensor arrived, builds the RoPE table and the launch graphs. */
+int b200_engine_finalize(b200_engine* e);
+/* Parses a GGUF file (gguf_parser.cpp:123) and does create + upload + finalize. desc_overrides may be
+ * NULL; when given, only kv_dtype, max_seqs, max_ctx, act_planes, device and the tp_* fields are read. */
+int b200_engine_load_gguf(const char* path, const b200_model_desc* desc_overrides, b200_engine** out);
+int b200_engine_get_desc(const b200_engine* e, b200_model_desc* out);
+int b200_engine_destroy(b200_engine* e);
+
+/* KVCache::clear_data (model.h:188-203) for one sequence slot. */
+int b200_kv_reset(b200_engine* e, int seq_slot);
+
+/* TinyLlamaModel::lookup_embedding (model_utils.cpp:11-182): one row of token_embd as FP32. */
+int b200_lookup_embedding(b200_engine* e, int token_id, float* host_out /* [hidden] */);
+
+/* TinyLlamaModel::forward(input, n_tokens, kv_cache, mask) (model.cpp:536-807) and
+ * forward_device(x_input_dev, pos, cache) (model.cpp:810-1090): one hidden-state vector in, the
+ * logits of the token at position pos of slot seq_slot out. host_x [hidden] is overwritten with
+ * the final residual stream like the reference's in-place `input`. */
+int b200_forward(b200_engine* e, int seq_slot, float* host_x, int pos, float* host_logits /* [vocab] */);
+
+/* Prompt ingestion: forward_cpu_batch + forward_cpu_logits_batch as driven by
+ * TinyLlamaSession::generate (api.cpp:603-641) / forward_device_batch_prefill (model.cpp:1526).
+ * Tokens occupy positions start_pos .. start_pos+n-1 of the slot. host_logits_last may be NULL. */
+int b200_prefill(b200_engine* e, int seq_slot, const int32_t* token_ids, int n, int start_pos,
+                 float* host_logits_last /* [vocab] */);
+
+/* One decode step for `batch` independent sequences: forward_device_batch_generation
+ * (model.cpp:1863) with the embedding lookup of the session loop (api.cpp:727) folded in.
+ * host_logits [batch][vocab] and argmax_out [batch] are each optional (NULL). argmax follows
+ * the greedy rule of the sampler: first maximum (api.cpp:134-136). */
+int b200_decode(b200_engine* e, int batch, const int32_t* token_ids, const int32_t* positions,
+                const int32_t* seq_slots, float* host_logits, int32_t* argmax_out);
+
+/* Greedy generation loop kept on the device (the session loop api.cpp:696-803 with temperature 0
+ * and no repetition penalty): `steps` decode steps for `batch` sequences starting from
+ * first_tokens at start_positions; each step's argmax feeds the next step without leaving HBM.
+ * out_tokens [steps][batch] receives the sampled ids; elapsed_ms (optional) the CUDA-event time
+ * of the loop. */
+int b200_generate_greedy(b200_engine* e, int batch, const int32_t* first_tokens,
+                         const int32_t* start_positions, const int32_t* seq_slots, int steps,
+                         int32_t* out_tokens, float* elapsed_ms);
+
+/* ---- op level, for parity tests (cuda_kernels.h op layer) ---- */
+/* Exact dequantizers: dequantize_q8_0_block / dequantize_q4_k_m / dequantize_q6_k
+ * (quantization.cpp:1047-1052, 171-221, 223-266); bit-exact, no fused multiply-add. */
+int b200_dequant(int ggml_type, const void* host_blocks, size_t n_blocks, float* host_out);
+/* y[b][r] = dot(W[r,:], x[b,:]) on the packed blocks: the fused kernel that replaces
+ * matvec_f32_f32_cuda (cuda_kernels.cu:291-314) / matvec_*_f32_vector_cpu (utils.cpp:293-397). */
+int b200_matvec(int ggml_type, const void* host_blocks, int64_t rows, int64_t cols, const float* host_x,
+                int batch, int act_planes, float* host_y);
+/* rmsnorm_vector_cuda (cuda_kernels.cu:209-253, 2499) */
+int b200_rmsnorm(const float* host_x, const float* host_w, int n, float eps, float* host_out);
+/* Decode attention of one new token over a cache of n_ctx earlier positions (attention_cuda,
+ * cuda_kernels.cu:1078 / 2523; INT8 form: quantizer of cuda_kernels.cu:1535-1606 with a softmax
+ * attention). q [n_heads][hd]; k_new, v_new [n_kv][hd] (already rotated); k_cache, v_cache
+ * [n_ctx][n_kv][hd] FP32 (quantized on upload when kv_dtype is I8). out [n_heads][hd]. */
+int b200_attention_decode(const float* q, const float* k_new, const float* v_new, const float* k_cache,
+                          const float* v_cache, int n_ctx, int n_heads, int n_kv_heads, int head_dim,
+                          int kv_dtype, int n_splits, float* out);
+
+/* Timing and counters for the benchmark harness. */
+int b200_engine_stats(const b200_engine* e, int64_t* kernel_launches_per_step, int64_t* weight_bytes,
+                      int64_t* kv_bytes_per_position);
+/* Repeats one kernel of the decode step alone (0 = the largest GEMV of a layer) `iters` times over
+ * distinct layers' weights and returns its mean CUDA-event duration and algorithmic bytes. */
+int b200_engine_time_kernel(b200_engine* e, int which, int iters, float* mean_us, int64_t* bytes_per_launch);
+
+/* Fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and shares the bytes). */
+int b200_nccl_unique_id(uint8_t* out128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,198 @@
+// Engine: weight residency, KV cache, the per-token launch sequence and its CUDA graph.
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "attn.cuh"
+#include "dequant.cuh"
+#include "gemv.cuh"
+#include "gguf.h"
+#include "misc.cuh"
+
+namespace b200 {
+
+thread_local std::string g_err;
+
+template <typename T>
+static T* dev_alloc(b200_engine* e, size_t n) {
+  void* p = nullptr;
+  CK(cudaMalloc(&p, std::max<size_t>(n * sizeof(T), 16)));
+  if (e) e->allocations.push_back(p);
+  return static_cast<T*>(p);
+}
+
+static void set_gemv_attrs() {
+  static bool done = false;
+  if (done) return;
+  const int maxb = 200 * 1024;
+  CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  done = true;
+}
+
+// Uploads one packed tensor; Q6_K / Q8_0 are split into aligned planes on the device.
+static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* host, size_t bytes, int64_t rows, int64_t cols,
+                          cudaStream_t stream) {
+  const int64_t be = type_block_elems(type), bb = type_block_bytes(type);
+  if (cols % be) throw std::runtime_error("tensor columns not a multiple of the block size");
+  const size_t nblk = (size_t)(rows * cols / be);
+  if (bytes != nblk * (size_t)bb) throw std::runtime_error("tensor byte count does not match rows x cols for its type");
+  t.type = type; t.rows = rows; t.cols = cols; t.bytes = bytes;
+  t.base = dev_alloc<uint8_t>(e, bytes + 256);
+  if (type == T_Q6_K || type == T_Q8_0) {
+    uint8_t* stage = nullptr;
+    CK(cudaMalloc((void**)&stage, bytes));
+    CK(cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, stream));
+    const size_t nthreads = bytes;
+    const unsigned grid = (unsigned)((nthreads + 255) / 256);
+    if (type == T_Q6_K) {
+      split_q6_k_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
+      t.qh = t.base + nblk * 128; t.sc = t.base + nblk * 192; t.d = t.base + nblk * 208;
+    } else {
+      split_q8_0_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
+      t.d = t.base + nblk * 32;
+    }
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(stream));
+    CK(cudaFree(stage));
+  } else {
+    CK(cudaMemcpyAsync(t.base, host, bytes, cudaMemcpyHostToDevice, stream));
+    CK(cudaStreamSynchronize(stream));
+  }
+}
+
+static GemvSeg seg_of(const DevTensor& t) {
+  GemvSeg s;
+  s.w = t.base; s.qh = t.qh; s.sc = t.sc; s.d = t.d; s.type = t.type; s.rows = (int)t.rows;
+  return s;
+}
+
+static int gemv_grid(const b200_engine* e, int npairs) {
+  return std::max(1, std::min((npairs + 7) / 8, e->num_sms * 2));
+}
+
+static void launch_gemv(const b200_engine* e, const GemvParams& p, int batch, int grid_x, cudaStream_t st) {
+  const size_t smem = act_smem_bytes(p.K, e->P);
+  dim3 grid(grid_x, batch);
+  if (e->P == 2) gemv_kernel<2><<<grid, 256, smem, st>>>(p);
+  else gemv_kernel<3><<<grid, 256, smem, st>>>(p);
+  CK(cudaGetLastError());
+}
+
+static int attn_nsplit(const b200_engine* e, int batch) {
+  int want = (2 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
+  return std::max(1, std::min(want, 32));
+}
+
+// The launch sequence of one decode step for `batch` sequences (also what gets captured).
+// Per layer: [RMSNorm + QKV + RoPE] -> [KV append + attention] -> [O proj + residual] ->
+// [RMSNorm + gate/up + SwiGLU] -> [down proj + residual]; then [RMSNorm + lm_head + argmax
+// partials] and token selection. Returns the number of kernel launches.
+static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, bool with_embed, int* head_ctas_out) {
+  int launches = 0;
+  const int H = e->H, F = e->F, KVD = e->KVD;
+  const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
+  if (with_embed) {
+    embed_kernel<<<batch, 256, 0, st>>>(e->d_tokens, e->tok_embd.f32(), e->d_h, H, e->V);
+    CK(cudaGetLastError());
+    ++launches;
+  }
+  for (int l = 0; l < e->L; ++l) {
+    const LayerW& w = e->layers[l];
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wq); p.seg[1] = seg_of(w.wk); p.seg[2] = seg_of(w.wv); p.nseg = 3;
+      p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
+      p.y = e->d_q; p.y_stride = H; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
+      p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
+      launch_gemv(e, p, batch, gemv_grid(e, (H + 2 * KVD) / 2), st);
+      ++launches;
+    }
+    {
+      AttnParams a{};
+      a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = H; a.kvn_stride = 2 * KVD;
+      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+      a.positions = e->d_positions; a.slots = e->d_slots;
+      a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
+      a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
+      a.out = e->d_attn; a.out_stride = H; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      const size_t smem = attn_smem_bytes(e->hd, e->max_ctx, nsplit, 4);
+      dim3 grid(nsplit, e->nq, batch);
+      if (e->desc.kv_dtype == B200_KV_I8) attn_decode_kernel<true><<<grid, 128, smem, st>>>(a);
+      else attn_decode_kernel<false><<<grid, 128, smem, st>>>(a);
+      CK(cudaGetLastError());
+      ++launches;
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = H; p.x = e->d_attn; p.x_stride = H; p.epi = EPI_RESID;
+      p.y = e->d_h; p.y_stride = H;
+      launch_gemv(e, p, batch, gemv_grid(e, H / 2), st);
+      ++launches;
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wgate); p.seg[1] = seg_of(w.wup); p.nseg = 2;
+      p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
+      p.y = e->d_act; p.y_stride = F;
+      launch_gemv(e, p, batch, gemv_grid(e, F), st);
+      ++launches;
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = EPI_RESID;
+      p.y = e->d_h; p.y_stride = H;
+      launch_gemv(e, p, batch, gemv_grid(e, H / 2), st);
+      ++launches;
+    }
+  }
+  {
+    GemvParams p{};
+    p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->d_h; p.x_stride = H;
+    p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE;
+    p.y = e->d_logits; p.y_stride = e->V;
+    const int grid = std::min(gemv_grid(e, e->V / 2), e->amax_cap);
+    p.amax_val = e->d_amax_val; p.amax_idx = e->d_amax_idx;
+    launch_gemv(e, p, batch, grid, st);
+    ++launches;
+    if (head_ctas_out) *head_ctas_out = grid;
+    SelectParams s{};
+    s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid; s.batch = batch;
+    s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
+    s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
+    select_kernel<<<1, 256, 0, st>>>(s);
+    CK(cudaGetLastError());
+    ++launches;
+  }
+  return launches;
+}
+
+static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {
+  const int key = batch * 2 + (with_embed ? 1 : 0);
+  auto it = e->graphs.find(key);
+  if (it != e->graphs.end()) return it->second;
+  StepGraph g;
+  g.nsplit = attn_nsplit(e, batch);
+  cudaGraph_t graph = nullptr;
+  CK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+  try {
+    g.launches = enqueue_step(e, batch, g.nsplit, e->stream, with_embed, &g.head_ctas);
+  } catch (...) {
+    cudaStreamEndCapture(e->stream, &graph);
+    if (graph) cudaGraphDestroy(graph);
+    throw;
+  }
+  CK(cudaStreamEndCapture(e->stream, &graph));
+  CK(cudaGraphInstantiate(&g.exec, graph, 0));
+  CK(cudaGraphDestroy(graph));
+  return e->graphs.emplace(key, g).first->second;
+}
+
+}  // namespace b200
+
+#include "engine_abi.inc"

@@ -1,0 +1,81 @@
+// Engine state behind the C ABI: device-resident packed weights, KV cache, step buffers and the
+// captured launch graphs of one decode step.
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/b200llama.h"
+#include "common.cuh"
+
+namespace b200 {
+
+struct DevTensor {
+  int type = -1;
+  int64_t rows = 0, cols = 0;
+  uint8_t* base = nullptr;  // Q4_K blocks / Q6_K ql plane / Q8_0 qs plane / F32 data
+  uint8_t* qh = nullptr;
+  uint8_t* sc = nullptr;
+  uint8_t* d = nullptr;
+  size_t bytes = 0;
+  bool present() const { return base != nullptr; }
+  const float* f32() const { return reinterpret_cast<const float*>(base); }
+};
+
+struct LayerW {
+  DevTensor attn_norm, wq, wk, wv, wo, ffn_norm, wgate, wup, wdown;
+  void* k_cache = nullptr;
+  void* v_cache = nullptr;
+  float* k_scale = nullptr;
+  float* v_scale = nullptr;
+};
+
+struct StepGraph {
+  cudaGraphExec_t exec = nullptr;
+  int nsplit = 1;
+  int head_ctas = 0;
+  int launches = 0;
+};
+
+}  // namespace b200
+
+struct b200_engine {
+  b200_model_desc desc{};
+  int H = 0, F = 0, nq = 0, nkv = 0, L = 0, V = 0, hd = 0, KVD = 0, max_ctx = 0, max_seqs = 0, P = 3;
+  int num_sms = 148;
+  bool finalized = false;
+  cudaStream_t stream = nullptr;
+  std::vector<b200::LayerW> layers;
+  b200::DevTensor tok_embd, out_norm, out_w;
+  float* rope = nullptr;
+  // step buffers
+  int* d_tokens = nullptr;
+  int* d_positions = nullptr;
+  int* d_slots = nullptr;
+  int* d_argmax = nullptr;
+  int* d_step = nullptr;
+  int* d_forced = nullptr;
+  int* d_forced_steps = nullptr;
+  int forced_cap = 0;
+  int* d_log = nullptr;
+  int log_cap = 0;
+  float* d_h = nullptr;
+  float* d_q = nullptr;
+  float* d_kvnew = nullptr;
+  float* d_attn = nullptr;
+  float* d_act = nullptr;
+  float* d_logits = nullptr;
+  float* d_amax_val = nullptr;
+  int* d_amax_idx = nullptr;
+  int amax_cap = 0;
+  float* d_part_o = nullptr;
+  float* d_part_ml = nullptr;
+  int* d_tickets = nullptr;
+  size_t part_cap = 0;  // floats in d_part_o
+  float* h_logits_pinned = nullptr;
+  int* h_ints_pinned = nullptr;
+  std::map<int, b200::StepGraph> graphs;
+  int64_t weight_bytes = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::vector<void*> allocations;
+};

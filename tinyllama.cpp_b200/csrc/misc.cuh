@@ -1,0 +1,88 @@
+// Small kernels around the layer loop: embedding gather and greedy token selection.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+// TinyLlamaModel::lookup_embedding for an FP32 table (reference model_utils.cpp:11-182):
+// h[b][:] = token_embd[tokens[b]][:]. grid.x = batch.
+__global__ void embed_kernel(const int* __restrict__ tokens, const float* __restrict__ embd, float* __restrict__ h, int H, int vocab) {
+  const int b = blockIdx.x;
+  int tok = tokens[b];
+  tok = min(max(tok, 0), vocab - 1);
+  const float4* src = reinterpret_cast<const float4*>(embd + (size_t)tok * H);
+  float4* dst = reinterpret_cast<float4*>(h + (size_t)b * H);
+  for (int i = threadIdx.x; i < H / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// Greedy sampling (reference api.cpp:134-136: first maximum) from the per-CTA partials the
+// lm_head kernel left, then bookkeeping for the next step: tokens[b] <- chosen (or the forced
+// token while a prompt is being replayed), positions[b] += 1, and the id is appended to the
+// step log. One block; warp w handles sequences w, w+nwarps, ...
+struct SelectParams {
+  const float* amax_val;  // [batch][nparts]
+  const int* amax_idx;
+  int nparts;
+  int batch;
+  int* tokens;            // [batch] in: this step's token, out: next step's
+  int* positions;         // [batch]
+  int* argmax_out;        // [batch] argmax of this step's logits
+  int* step_counter;      // steps done since the loop was armed
+  const int* forced;      // [forced_steps][batch] tokens to feed instead of the argmax, or nullptr
+  const int* forced_steps;// device scalar
+  int* log;               // [log_cap][batch]
+  int log_cap;
+};
+
+__global__ void select_kernel(const SelectParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int step = *p.step_counter;
+  const int fsteps = p.forced ? *p.forced_steps : 0;
+  for (int b = warp; b < p.batch; b += nwarps) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < p.nparts; i += 32) {
+      const float v = p.amax_val[(size_t)b * p.nparts + i];
+      const int idx = p.amax_idx[(size_t)b * p.nparts + i];
+      if (v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      p.argmax_out[b] = bi;
+      int next = bi;
+      if (step + 1 < fsteps) next = p.forced[(size_t)(step + 1) * p.batch + b];
+      p.tokens[b] = next;
+      p.positions[b] += 1;
+      if (step < p.log_cap) p.log[(size_t)step * p.batch + b] = bi;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *p.step_counter = step + 1;
+}
+
+// Standalone RMSNorm for the op-level entry point (reference utils.cpp:648-673).
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out, int n, float eps) {
+  __shared__ double red[33];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  double ss = 0.0;
+  for (int i = tid; i < n; i += blockDim.x) ss += (double)x[i] * (double)x[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (tid == 0) {
+    double t = 0.0;
+    for (int wv = 0; wv < nwarps; ++wv) t += red[wv];
+    red[32] = t;
+  }
+  __syncthreads();
+  const float f = 1.0f / sqrtf((float)(red[32] / (double)n) + eps);
+  for (int i = tid; i < n; i += blockDim.x) out[i] = x[i] * f * w[i];
+}
+
+}  // namespace b200
