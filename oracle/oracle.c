@@ -217,6 +217,50 @@ void orc_kv_quantize_i8(const float* x, int n, int8_t* q, float* scale) {
   }
 }
 
+
+/* Standalone form of the attention step of forward_token (model.cpp:632-663): one new token
+ * attending to rows 0..T-1 of kc / vc ([T][n_kv][hd], the last row being the new token).
+ * With kv_int8 every row goes through orc_kv_quantize_i8 and back first ("restated oracle"). */
+void orc_attention_decode(const float* q, const float* kc, const float* vc, int T, int nq, int nkv, int hd,
+                          int kv_int8, float* out) {
+  const int KV = nkv * hd;
+  float* k = (float*)malloc(sizeof(float) * (size_t)T * KV);
+  float* v = (float*)malloc(sizeof(float) * (size_t)T * KV);
+  memcpy(k, kc, sizeof(float) * (size_t)T * KV);
+  memcpy(v, vc, sizeof(float) * (size_t)T * KV);
+  if (kv_int8) {
+    int8_t* tmp = (int8_t*)malloc((size_t)hd);
+    for (size_t r = 0; r < (size_t)T * nkv; ++r) {
+      float sc;
+      orc_kv_quantize_i8(k + r * hd, hd, tmp, &sc);
+      for (int d = 0; d < hd; ++d) k[r * hd + d] = (float)tmp[d] * sc;
+      orc_kv_quantize_i8(v + r * hd, hd, tmp, &sc);
+      for (int d = 0; d < hd; ++d) v[r * hd + d] = (float)tmp[d] * sc;
+    }
+    free(tmp);
+  }
+  float* scores = (float*)malloc(sizeof(float) * (size_t)T);
+  const float att_scale = 1.0f / sqrtf((float)hd);
+  for (int h = 0; h < nq; ++h) {
+    const float* qh = q + h * hd;
+    const int kvh = h / (nq / nkv);
+    for (int t = 0; t < T; ++t) {
+      const float* kr = k + ((size_t)t * nkv + kvh) * hd;
+      float s = 0.0f;
+      for (int d = 0; d < hd; ++d) s += qh[d] * kr[d];
+      scores[t] = s * att_scale;
+    }
+    orc_softmax(scores, scores, T);
+    float* o = out + h * hd;
+    for (int d = 0; d < hd; ++d) o[d] = 0.0f;
+    for (int t = 0; t < T; ++t) {
+      const float* vr = v + ((size_t)t * nkv + kvh) * hd;
+      for (int d = 0; d < hd; ++d) o[d] += scores[t] * vr[d];
+    }
+  }
+  free(k); free(v); free(scores);
+}
+
 /* ------------------------------------------------------------------------------------ */
 typedef struct {
   float *attn_norm, *ffn_norm, *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;

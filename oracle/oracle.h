@@ -29,6 +29,8 @@ void orc_silu(const float* x, float* out, int n);
 void orc_rope_table(float theta, int head_dim, int max_pos, float* table /* [max_pos][hd/2][2] */);
 void orc_rope_vector(float* x, int n_heads, int head_dim, int pos, const float* table, int max_pos);
 void orc_kv_quantize_i8(const float* x, int n, int8_t* q, float* scale);
+void orc_attention_decode(const float* q, const float* kc, const float* vc, int T, int nq, int nkv, int hd,
+                          int kv_int8, float* out);
 
 typedef struct orc_model orc_model;
 orc_model* orc_model_create(int hidden, int ffn, int n_heads, int n_kv_heads, int n_layers, int vocab,

@@ -46,6 +46,8 @@ def oracle():
         L.orc_rope_table.argtypes = [ctypes.c_float, _i, _i, _vp]
         L.orc_rope_vector.argtypes = [_vp, _i, _i, _i, _vp, _i]
         L.orc_kv_quantize_i8.argtypes = [_vp, _i, _vp, _vp]
+        L.orc_attention_decode.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]
+        L.orc_attention_decode.restype = None
         L.orc_model_create.restype = _vp
         L.orc_model_create.argtypes = [_i] * 7 + [ctypes.c_float, ctypes.c_float, _i, _i]
         L.orc_model_destroy.argtypes = [_vp]
@@ -110,6 +112,14 @@ def matvec_f32(which, w, x):
     else:
         ref().ref_matvec_f32(_p(w), _p(x), _p(y), rows, cols)
     return y
+
+
+def attention_decode(q, kc, vc, nq, nkv, hd, kv_int8=False):
+    q, kc, vc = (np.ascontiguousarray(a, np.float32) for a in (q, kc, vc))
+    T = kc.size // (nkv * hd)
+    out = np.empty(nq * hd, np.float32)
+    oracle().orc_attention_decode(_p(q), _p(kc), _p(vc), T, nq, nkv, hd, int(kv_int8), _p(out))
+    return out
 
 
 def rope_table(theta, head_dim, max_pos):

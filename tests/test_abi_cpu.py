@@ -1,0 +1,54 @@
+"""CPU-only checks of the boundary: the shared library loads, exports every symbol the header
+declares, and refuses to compute without a GPU (there is no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200llama.h")).read()
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_python_mirror_agree(pkg):
+    assert declared_symbols() == sorted(pkg.api.EXPORTS)
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg.api.lib()
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+
+
+def test_desc_struct_layout(pkg):
+    # 16 int32/float fields + 128 bytes of NCCL id, no padding
+    assert ctypes.sizeof(pkg.api.ModelDesc) == 16 * 4 + 128
+
+
+def test_no_cpu_fallback(pkg):
+    if pkg.api.device_count() > 0:
+        pytest.skip("a GPU is present")
+    with pytest.raises(pkg.B200Error, match="no CUDA device"):
+        pkg.api.dequant(8, np.zeros(34, np.uint8), 1)
+    with pytest.raises(pkg.B200Error, match="no CUDA device"):
+        pkg.Engine.create(dict(pkg.synth.SHAPES["tiny"], eps=1e-5))
+
+
+def test_create_rejects_bad_dims(pkg):
+    bad = dict(pkg.synth.SHAPES["tiny"], eps=1e-5, hidden=250)
+    with pytest.raises(pkg.B200Error):
+        pkg.Engine.create(bad)
+
+
+def test_product_never_touches_oracle():
+    """Nothing under the package or the C ABI may reference the oracle folder."""
+    for root, _, files in os.walk(os.path.join(ROOT, "tinyllama.cpp_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h", ".inc")):
+                text = open(os.path.join(root, f), errors="replace").read()
+                assert "oracle" not in text.lower(), os.path.join(root, f)

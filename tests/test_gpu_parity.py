@@ -1,0 +1,268 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the golden fixtures.
+
+Tolerances (stated here, used below):
+  dequantized blocks     bit-exact
+  matvec                 |y - ref| <= 1e-3 * max(|ref_i|, 1e-3 * max|ref|)   (ref = Kahan FP32 dot, utils.cpp:349-397)
+  logits                 <= 2e-2 absolute; greedy ids identical for 32 steps
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+TYPES = {"q8_0": 8, "q4_k": 12, "q6_k": 14}
+
+
+def rel_err(y, ref):
+    den = np.maximum(np.abs(ref), 1e-3 * np.abs(ref).max())
+    return float((np.abs(y - ref) / den).max())
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return np.load(os.path.join(GOLD, "ops.npz"))
+
+
+@pytest.fixture(scope="module")
+def tiny_gold():
+    return np.load(os.path.join(GOLD, "tiny_models.npz"))
+
+
+@pytest.mark.parametrize("name", list(TYPES))
+def test_dequant_bit_exact_golden_and_random(pkg, ops, name):
+    typ = TYPES[name]
+    blocks = ops[f"{name}_blocks"]
+    out = pkg.api.dequant(typ, blocks, blocks.size // ol.BLOCK_BYTES[typ])
+    assert np.array_equal(out.view(np.uint32), ops[f"{name}_out"].view(np.uint32))
+    rnd = np.random.default_rng(typ).integers(0, 256, 513 * ol.BLOCK_BYTES[typ], dtype=np.uint8)
+    out = pkg.api.dequant(typ, rnd, 513)
+    ref = ol.dequant("oracle", typ, rnd)
+    # random bytes include NaN / Inf scale fields: NaNs must sit in the same places (their payload
+    # bits are not defined by IEEE arithmetic), everything else must match bit for bit
+    assert np.array_equal(np.isnan(out), np.isnan(ref))
+    ok = ~np.isnan(ref)
+    assert np.array_equal(out.view(np.uint32)[ok], ref.view(np.uint32)[ok])
+    assert pkg.api.dequant(typ, np.zeros(0, np.uint8), 0).size == 0  # empty input
+
+
+@pytest.mark.parametrize("planes", [3, 2])
+@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("rows,cols", [(2, 256), (6, 512), (64, 4096), (130, 11008), (34, 1024)])
+def test_matvec_vs_kahan_dot(pkg, name, rows, cols, planes):
+    typ = TYPES[name]
+    w = pkg.synth.fill_normal(rows * cols, 77, rows + typ, 0.02)
+    blocks = pkg.synth.quantize(typ, w)
+    x = pkg.synth.fill_normal(cols, 78, cols, 1.0)
+    wd = ol.dequant("oracle", typ, blocks).reshape(rows, cols)
+    ref = ol.matvec_f32("oracle", wd, x)
+    y = pkg.api.matvec(typ, blocks, rows, cols, x, act_planes=planes)
+    err = rel_err(y, ref)
+    if planes == 3:
+        assert err <= 1e-3, err
+    else:  # 16-bit activations: looser floor, still 1e-3 on elements that are not near-cancelled
+        den = np.maximum(np.abs(ref), 1e-1 * np.abs(ref).max())
+        assert float((np.abs(y - ref) / den).max()) <= 1e-3
+
+
+def test_matvec_batch_and_edge_values(pkg):
+    rows, cols = 8, 512
+    w = pkg.synth.fill_normal(rows * cols, 5, 9, 0.02)
+    blocks = pkg.synth.quantize(12, w)
+    wd = ol.dequant("oracle", 12, blocks).reshape(rows, cols)
+    x = np.stack([pkg.synth.fill_normal(cols, 6, i + 1, 1.0) for i in range(3)])
+    x[1] = 0.0                      # all-zero activation vector
+    x[2, :256] = 0.0                # one all-zero 256-block
+    x[2, 300] = 1e4                 # outlier dominating its block's scale
+    y = pkg.api.matvec(12, blocks, rows, cols, x)
+    for b in range(3):
+        ref = ol.matvec_f32("oracle", wd, x[b])
+        assert np.all(np.abs(y[b] - ref) <= 1e-3 * np.maximum(np.abs(ref), 1e-3 * max(np.abs(ref).max(), 1e-30)))
+    assert not y[1].any()
+
+
+def test_rmsnorm(pkg):
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(4096).astype(np.float32) * 2
+    w = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float32)
+    ref = np.empty_like(x)
+    ol.oracle().orc_rmsnorm_vector(ol._p(x), ol._p(w), ol._p(ref), x.size, 1e-5)
+    out = pkg.api.rmsnorm(x, w, 1e-5)
+    assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("kv_i8", [False, True])
+@pytest.mark.parametrize("nq,nkv,hd,n_ctx,splits", [(4, 2, 64, 0, 1), (4, 2, 64, 1, 3), (8, 8, 128, 77, 4),
+                                                     (8, 2, 128, 300, 8), (4, 1, 32, 129, 5), (32, 4, 64, 1000, 6)])
+def test_attention_decode(pkg, kv_i8, nq, nkv, hd, n_ctx, splits):
+    rng = np.random.default_rng(n_ctx + nq)
+    q = rng.standard_normal(nq * hd).astype(np.float32)
+    kc = rng.standard_normal((n_ctx + 1, nkv, hd)).astype(np.float32)
+    vc = rng.standard_normal((n_ctx + 1, nkv, hd)).astype(np.float32)
+    if n_ctx > 2:
+        kc[1] = 0.0  # an all-zero row: INT8 scale falls back to 1.0
+    ref = ol.attention_decode(q, kc, vc, nq, nkv, hd, kv_int8=kv_i8)
+    out = pkg.api.attention_decode(q, kc[-1], vc[-1], kc[:-1], vc[:-1], nq, nkv, hd,
+                                   kv_dtype=pkg.KV_I8 if kv_i8 else pkg.KV_F32, n_splits=splits)
+    assert np.abs(out - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max())
+
+
+def run_greedy(eng, orc, first, steps, start=0):
+    tok, ids_e, ids_o, worst, margins = first, [], [], 0.0, []
+    for pos in range(start, start + steps):
+        logits, amax = eng.decode([tok], [pos])
+        ref = orc.decode(tok, pos)
+        worst = max(worst, float(np.abs(logits[0] - ref).max()))
+        ids_e.append(int(amax[0]))
+        ids_o.append(int(ref.argmax()))
+        top2 = np.sort(ref)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        assert int(amax[0]) == int(logits[0].argmax())
+        tok = ids_o[-1]
+    return ids_e, ids_o, worst, margins
+
+
+@pytest.mark.parametrize("planes", [3, 2])
+@pytest.mark.parametrize("scheme", [0, 1, 2, 3])
+def test_engine_decode_fp32_kv(pkg, tiny_models, tiny_gold, scheme, planes):
+    eng = pkg.Engine.from_gguf(tiny_models[scheme], kv_dtype=pkg.KV_F32, act_planes=planes)
+    orc = ol.OracleModel.from_gguf(tiny_models[scheme])
+    ids_e, ids_o, worst, margins = run_greedy(eng, orc, 7, 32)
+    assert worst <= 2e-2, worst
+    if planes == 3:  # 24-bit activations: the default, and the mode the greedy-id gate is defined on
+        assert ids_e == ids_o
+        assert ids_e[:24] == tiny_gold[f"s{scheme}_decode_ids"].tolist()
+        assert worst <= 1e-4, worst  # far inside the gate
+    else:  # 16-bit activations (speed option): ids may only differ where the oracle's top-2 gap is a near-tie
+        assert all(a == b or m < 1e-3 for a, b, m in zip(ids_e, ids_o, margins))
+    eng.close()
+
+
+@pytest.mark.parametrize("scheme", [0, 1])
+def test_engine_decode_int8_kv(pkg, tiny_models, scheme):
+    eng = pkg.Engine.from_gguf(tiny_models[scheme], kv_dtype=pkg.KV_I8)
+    orc = ol.OracleModel.from_gguf(tiny_models[scheme], kv_int8=True)
+    ids_e, ids_o, worst, _ = run_greedy(eng, orc, 3, 32)
+    assert worst <= 2e-2, worst
+    assert ids_e == ids_o
+    eng.close()
+
+
+@pytest.mark.parametrize("scheme", [0, 1])
+def test_engine_prefill_then_decode(pkg, tiny_models, tiny_gold, scheme):
+    eng = pkg.Engine.from_gguf(tiny_models[scheme])
+    prompt = tiny_gold[f"s{scheme}_prompt"]
+    logits = eng.prefill(prompt)
+    assert np.abs(logits - tiny_gold[f"s{scheme}_prefill_logits"]).max() <= 2e-2
+    tok, ids = int(logits.argmax()), []
+    for pos in range(40, 56):
+        ids.append(tok)
+        lg, amax = eng.decode([tok], [pos])
+        tok = int(amax[0])
+    assert ids == tiny_gold[f"s{scheme}_after_prefill_ids"].tolist()
+    eng.close()
+
+
+def test_generate_greedy_matches_stepwise_and_oracle(pkg, tiny_models):
+    eng = pkg.Engine.from_gguf(tiny_models[1], kv_dtype=pkg.KV_I8, max_seqs=3)
+    orc = ol.OracleModel.from_gguf(tiny_models[1], kv_int8=True, max_seqs=3)
+    firsts = [5, 400, 77]
+    out, ms = eng.generate_greedy(firsts, [0, 0, 0], 32)
+    assert ms > 0
+    for b, first in enumerate(firsts):
+        tok, ids = first, []
+        for pos in range(32):
+            tok = int(orc.decode(tok, pos, seq=b).argmax())
+            ids.append(tok)
+        assert out[:, b].tolist() == ids
+    # a second call continues from the caches it left
+    out2, _ = eng.generate_greedy(out[-1], [32, 32, 32], 8)
+    for b in range(3):
+        tok = int(out[-1, b])
+        for pos in range(32, 40):
+            tok = int(orc.decode(tok, pos, seq=b).argmax())
+            assert out2[pos - 32, b] == tok
+    eng.close()
+
+
+def test_batch_decode_ragged_positions_and_slots(pkg, tiny_models):
+    """Independent sequences at different positions, mapped to shuffled KV slots."""
+    eng = pkg.Engine.from_gguf(tiny_models[3], max_seqs=4)
+    orc = ol.OracleModel.from_gguf(tiny_models[3], max_seqs=4)
+    rng = np.random.default_rng(5)
+    lens = [3, 17, 1, 40]
+    slots = [2, 0, 3, 1]
+    last = []
+    for s, n in zip(slots, lens):
+        ids = rng.integers(0, 512, n)
+        eng.prefill(ids, slot=s)
+        orc.prefill(ids, seq=s)
+        last.append(int(ids[-1]))
+    toks = [9, 10, 11, 12]
+    logits, amax = eng.decode(toks, lens, slots=slots)
+    for b in range(4):
+        ref = orc.decode(toks[b], lens[b], seq=slots[b])
+        assert np.abs(logits[b] - ref).max() <= 2e-2
+        assert int(amax[b]) == int(ref.argmax())
+    eng.close()
+
+
+def test_forward_from_hidden_state(pkg, tiny_models):
+    """b200_forward mirrors TinyLlamaModel::forward: hidden vector in, logits out, input updated in place."""
+    eng = pkg.Engine.from_gguf(tiny_models[1])
+    orc = ol.OracleModel.from_gguf(tiny_models[1])
+    x = eng.lookup_embedding(42)
+    g = pkg.gguf.GGUF(tiny_models[1])
+    emb = np.frombuffer(g.tensors["token_embd.weight"]["data"], np.float32).reshape(512, 256)
+    assert np.array_equal(x, emb[42])
+    logits = eng.forward(x, 0)
+    ref = orc.decode(42, 0)
+    assert np.abs(logits - ref).max() <= 2e-2
+    assert np.abs(x - orc.layer_trace()[-1]).max() <= 1e-4  # residual stream after the last layer
+    eng.close()
+
+
+def test_kv_reset_and_errors(pkg, tiny_models):
+    eng = pkg.Engine.from_gguf(tiny_models[0], max_ctx=16)
+    a, _ = eng.decode([1], [0])
+    eng.decode([2], [1])
+    eng.kv_reset(0)
+    b, _ = eng.decode([1], [0])
+    assert np.array_equal(a, b)
+    with pytest.raises(pkg.B200Error, match="exceeds the KV capacity"):
+        eng.decode([1], [16])
+    with pytest.raises(pkg.B200Error, match="token id out of range"):
+        eng.decode([512], [0])
+    with pytest.raises(pkg.B200Error, match="batch out of range"):
+        eng.decode([1, 2], [0, 0])
+    with pytest.raises(pkg.B200Error):
+        eng.prefill(np.arange(17))
+    eng.close()
+    with pytest.raises(pkg.B200Error, match="cannot open"):
+        pkg.Engine.from_gguf("/nonexistent/model.gguf")
+
+
+def test_upload_tensor_path_and_validation(pkg, tiny_models):
+    """create + upload_tensor + finalize gives the same engine as load_gguf; malformed input is refused."""
+    g = pkg.gguf.GGUF(tiny_models[1])
+    eng = pkg.Engine.create(g.config())
+    with pytest.raises(pkg.B200Error, match="unknown tensor name"):
+        eng.upload_tensor("blk.9.attn_q.weight", 12, np.zeros(144, np.uint8), 1, 256)
+    t = g.tensors["blk.0.attn_q.weight"]
+    with pytest.raises(pkg.B200Error, match="byte count"):
+        eng.upload_tensor("blk.0.attn_q.weight", 12, t["data"][:-144], t["rows"], t["cols"])
+    with pytest.raises(pkg.B200Error):
+        eng.finalize()  # tensors missing
+    for name in g.order:
+        t = g.tensors[name]
+        eng.upload_tensor(name, t["type"], t["data"], t["rows"], t["cols"])
+    eng.finalize()
+    ref = pkg.Engine.from_gguf(tiny_models[1])
+    a, _ = eng.decode([5], [0])
+    b, _ = ref.decode([5], [0])
+    assert np.array_equal(a, b)
+    eng.close()
+    ref.close()
