@@ -1,0 +1,254 @@
+#!/usr/bin/env python
+"""Decode benchmark: tokens/s of the per-token transformer forward over GGUF K-quant weights.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl b200|reference]
+
+A step is one decode step (one new token for every sequence of the batch). The default workload is
+the Llama-2-7B-shaped Q4_K_M-style model at batch 1 with a 1024-token prompt and an INT8 KV cache.
+Weights are synthetic (seeded N(0, 0.02), quantized by the package's writer); prompts are seeded
+uniform token ids. One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__  # noqa: E402
+
+WORKLOADS = {
+    # name: (shape, scheme, batch, prompt_len, kv)
+    "c1-tinyllama-q8_0-bs1": ("tinyllama-1.1b", 0, 1, 128, "f32"),
+    "c2-tinyllama-q4km-bs1": ("tinyllama-1.1b", 1, 1, 512, "i8"),
+    "c3-llama2-7b-q4km-bs1": ("llama2-7b", 1, 1, 1024, "i8"),
+    "c3-llama2-7b-q4km-bs16": ("llama2-7b", 1, 16, 1024, "i8"),
+    "tiny": ("tiny", 1, 1, 16, "i8"),
+}
+DEFAULT_WORKLOAD = "c3-llama2-7b-q4km-bs1"
+METRIC = "decode tokens/s (Llama-2-7B Q4_K_M, bs=1) and % of HBM roofline at 1/2/4/8 B200"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._stop_evt = index, [], threading.Event()
+
+    def run(self):
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def finish(self):
+        self._stop_evt.set()
+        self.join(timeout=6)
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in self.rows)]
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def model_path(pkg, shape, scheme):
+    base = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else "/tmp"
+    path = os.path.join(base, f"b200_synth_{shape}_s{scheme}.gguf")
+    if not os.path.exists(path):
+        tmp = path + f".{os.getpid()}.tmp"
+        pkg.synth.write_gguf(tmp, shape, scheme=scheme)
+        os.replace(tmp, path)
+    return path
+
+
+def prompts(batch, n, vocab):
+    return [np.random.Generator(np.random.PCG64(4321 + s)).integers(0, vocab, n).astype(np.int32) for s in range(batch)]
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def cpu_reference_tokens_per_s(path, budget_s, max_tokens):
+    """Times the reference's own CPU forward (oracle/_ref) on the same model file: decode steps from
+    an empty context, as many as fit the time budget (at least one)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    m = ol.RefModel(path)
+    tok, n, t0 = 5, 0, time.perf_counter()
+    while n < max_tokens:
+        tok = int(m.decode(tok, n).argmax())
+        n += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return n / dt, cores, n, dt
+
+
+def run_reference(args, shape, scheme, batch, prompt_len):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    pkg = __graft_entry__.load_package()
+    path = model_path(pkg, shape, scheme)
+    tps, cores, n, dt = cpu_reference_tokens_per_s(path, budget_s=150.0, max_tokens=max(1, args.steps))
+    sample = f"{n} decode steps of the full model from an empty context (batch 1), {dt:.1f} s"
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--planes", type=int, default=3, choices=[2, 3])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    shape, scheme, batch, prompt_len, kv = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, shape, scheme, batch, prompt_len)
+
+    rank, local_rank, world = dist_env()
+    warmup = max(args.warmup, 3)
+    pkg = __graft_entry__.load_package()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    # model file: written once per box (rank 0), then shared
+    if rank == 0:
+        path = model_path(pkg, shape, scheme)
+    if dist:
+        dist.barrier()
+    path = model_path(pkg, shape, scheme)
+    t_load = time.perf_counter()
+    eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if kv == "i8" else pkg.KV_F32, max_seqs=batch,
+                               max_ctx=prompt_len + args.steps + warmup + 80, act_planes=args.planes, device=local_rank)
+    t_load = time.perf_counter() - t_load
+    vocab = eng.vocab
+    pr = prompts(batch, prompt_len, vocab)
+    t_prefill = time.perf_counter()
+    first = []
+    for s in range(batch):
+        first.append(int(eng.prefill(pr[s], slot=s).argmax()))
+    t_prefill = time.perf_counter() - t_prefill
+    pos = prompt_len
+
+    # ---- warm-up, then the timed device-resident loop ----
+    out, _ = eng.generate_greedy(first, [pos] * batch, warmup)
+    pos += warmup
+    nxt = out[-1].copy()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    out, ms = eng.generate_greedy(nxt, [pos] * batch, args.steps)
+    clocks = sampler.finish()
+    pos += args.steps
+    if dist:
+        import torch
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    tokens_per_s = world * batch * args.steps / (ms / 1000.0)
+
+    # ---- end to end through the C ABI with host buffers: token ids in, logits out, host argmax ----
+    e2e_steps = min(args.steps, 64)
+    toks = out[-1].copy()
+    eng.decode(toks, [pos] * batch)  # graph already warm; one untimed call
+    pos += 1
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        logits, _ = eng.decode(toks, [pos + i] * batch, want_logits=True, want_argmax=False)
+        toks = logits.argmax(axis=1).astype(np.int32)
+    e2e_dt = time.perf_counter() - t0
+    e2e_tps = world * batch * e2e_steps / e2e_dt
+
+    # ---- roofline of the dominant kernel (the fused dequant-GEMV), each kind timed by itself ----
+    st = eng.stats()
+    L = eng.desc.num_hidden_layers
+    kinds = {"gate_up_swiglu": (0, L), "qkv_rope": (1, L), "o_proj": (2, L), "down_proj": (3, L), "lm_head": (4, 1)}
+    peak, peak_src = peaks()
+    ksum_b = ksum_t = 0.0
+    kern = {}
+    for name, (which, per_step) in kinds.items():
+        us, nbytes = eng.time_kernel(which, max(2 * L, 32))
+        kern[name] = {"us": round(us, 3), "bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1), "launches_per_step": per_step}
+        ksum_b += nbytes * per_step
+        ksum_t += us * per_step
+    gemv_launches = sum(v[1] for v in kinds.values())
+    achieved = ksum_b / ksum_t / 1e3  # GB/s
+    ctx_mid = prompt_len + warmup + args.steps / 2.0
+    step_bytes = st["weight_bytes"] + batch * 4 * eng.hidden + batch * ctx_mid * st["kv_bytes_per_position"]
+    step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "traffic": None, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
+                "bytes_per_launch": int(ksum_b / gemv_launches), "us_per_launch": round(ksum_t / gemv_launches, 3),
+                "kinds": kern, "step_bytes": int(step_bytes), "step_GBps": round(step_gbps, 1),
+                "step_frac_of_measured_peak": round(step_gbps / peak, 4), "step_frac_of_8TBps": round(step_gbps / 8000.0, 4)}
+
+    line = {"metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": f"i{8 * args.planes} activations x packed int weights, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len, "kv_cache": kv,
+                       "context_during_timing": [prompt_len + warmup, prompt_len + warmup + args.steps],
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": "weights read per step (GBs) exceed the 126 MB L2; no flush needed",
+                       "act_planes": args.planes, "load_s": round(t_load, 2), "prefill_s": round(t_prefill, 2)},
+            "e2e": {"value": e2e_tps, "unit": "tokens/s", "h2d_bytes_per_step": 12 * batch,
+                    "d2h_bytes_per_step": 4 * vocab * batch, "steps": e2e_steps},
+            "gpu_launches": st["launches_per_step"] * args.steps, "clocks": clocks, "roofline": roofline}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libref_cpu.so")):
+        eng.close()
+        tps, cores, n, dt = cpu_reference_tokens_per_s(path, budget_s=20.0, max_tokens=4)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference",
+                                "sample": f"{n} decode steps of the same model file from an empty context, {dt:.1f} s"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
