@@ -53,7 +53,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) 
   int chunk = (T + prm.nsplit - 1) / prm.nsplit;
   chunk = (chunk + 31) & ~31;
   const int t0 = split * chunk, t1 = min(T, t0 + chunk);
-  const int cap = ((prm.max_ctx + prm.nsplit - 1) / prm.nsplit + 31) & ~31;  // max positions per split
 
   float* q_s = sm;               // [hd]
   float* kn_s = q_s + hd;        // [hd] new K row as the cache will hold it (dequantised when INT8)

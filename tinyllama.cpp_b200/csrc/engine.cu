@@ -72,16 +72,30 @@ static GemvSeg seg_of(const DevTensor& t) {
   return s;
 }
 
-static int gemv_grid(const b200_engine* e, int npairs) {
-  return std::max(1, std::min((npairs + 7) / 8, e->num_sms * 2));
-}
-
-static void launch_gemv(const b200_engine* e, const GemvParams& p, int batch, int grid_x, cudaStream_t st) {
+// Fills in the tile count, checks the launch's shape rules and starts the kernel with one
+// persistent CTA per SM (fewer when there are fewer tiles). Returns the grid width.
+static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream_t st) {
+  if (p.K % 256) throw std::runtime_error("gemv: K must be a multiple of 256");
+  if (p.epi == EPI_SWIGLU) {
+    if (p.nseg != 2 || p.seg[0].rows != p.seg[1].rows || p.seg[0].type != p.seg[1].type)
+      throw std::runtime_error("gemv: gate and up must have the same shape and block type");
+    p.ntiles = (p.seg[0].rows + 7) / 8;
+  } else {
+    int rows = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+      if (s + 1 < p.nseg && p.seg[s].rows % 16) throw std::runtime_error("gemv: segment rows must be a multiple of 16");
+      rows += p.seg[s].rows;
+    }
+    p.ntiles = (rows + 15) / 16;
+  }
   const size_t smem = act_smem_bytes(p.K, e->P);
-  dim3 grid(grid_x, batch);
-  if (e->P == 2) gemv_kernel<2><<<grid, 256, smem, st>>>(p);
-  else gemv_kernel<3><<<grid, 256, smem, st>>>(p);
+  if (smem > 200 * 1024) throw std::runtime_error("gemv: input dimension too large for the shared-memory activation image");
+  const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
+  dim3 grid(gx, batch);
+  if (e->P == 2) gemv_kernel<2><<<grid, GEMV_THREADS, smem, st>>>(p);
+  else gemv_kernel<3><<<grid, GEMV_THREADS, smem, st>>>(p);
   CK(cudaGetLastError());
+  return gx;
 }
 
 static int attn_nsplit(const b200_engine* e, int batch) {
@@ -110,7 +124,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
       p.y = e->d_q; p.y_stride = H; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
       p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
-      launch_gemv(e, p, batch, gemv_grid(e, (H + 2 * KVD) / 2), st);
+      launch_gemv(e, p, batch, st);
       ++launches;
     }
     {
@@ -132,7 +146,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = H; p.x = e->d_attn; p.x_stride = H; p.epi = EPI_RESID;
       p.y = e->d_h; p.y_stride = H;
-      launch_gemv(e, p, batch, gemv_grid(e, H / 2), st);
+      launch_gemv(e, p, batch, st);
       ++launches;
     }
     {
@@ -140,14 +154,14 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.seg[0] = seg_of(w.wgate); p.seg[1] = seg_of(w.wup); p.nseg = 2;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
       p.y = e->d_act; p.y_stride = F;
-      launch_gemv(e, p, batch, gemv_grid(e, F), st);
+      launch_gemv(e, p, batch, st);
       ++launches;
     }
     {
       GemvParams p{};
       p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = EPI_RESID;
       p.y = e->d_h; p.y_stride = H;
-      launch_gemv(e, p, batch, gemv_grid(e, H / 2), st);
+      launch_gemv(e, p, batch, st);
       ++launches;
     }
   }
@@ -156,9 +170,8 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->d_h; p.x_stride = H;
     p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE;
     p.y = e->d_logits; p.y_stride = e->V;
-    const int grid = std::min(gemv_grid(e, e->V / 2), e->amax_cap);
     p.amax_val = e->d_amax_val; p.amax_idx = e->d_amax_idx;
-    launch_gemv(e, p, batch, grid, st);
+    const int grid = launch_gemv(e, p, batch, st);
     ++launches;
     if (head_ctas_out) *head_ctas_out = grid;
     SelectParams s{};

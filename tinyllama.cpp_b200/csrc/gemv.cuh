@@ -1,15 +1,26 @@
-// Fused dequant-matvec over packed Q8_0 / Q4_K / Q6_K blocks for batch-1 style decode.
+// Fused dequant-matvec over packed Q8_0 / Q4_K / Q6_K blocks for decode (one activation vector
+// per launch column).
 //
-// Arithmetic: the activation vector is quantised once per CTA into P signed byte-planes
-// (x ~ sx[blk] * x_int, x_int a (8P)-bit integer per element, one scale per 256 elements;
-// P = 3 gives 24-bit activations, i.e. FP32-grade). Weights stay integers: every dot product
-// over a quantisation sub-block is an exact integer sum built from dp4a, the sub-block's
-// integer scale is applied with an integer multiply-add, and only one float multiply per
-// (row, 64..128 weights) touches the block's fp16 scale. Minimum/offset terms use per-sub-block
-// sums of the activations prepared in shared memory. Rows are reduced with warp shuffles.
+// Arithmetic. The activation vector is quantised once per CTA into P balanced base-256 digit
+// planes (x ~ sx[blk] * x_int, x_int = sum_p digit_p * 256^p, every digit a signed byte, one scale
+// per 256 elements; P = 3 gives 24-bit activations, i.e. FP32-grade). Weights stay the integers
+// that are stored in the blocks. A warp owns a tile of 16 output rows and walks along K one
+// 256-element block at a time; every 32 elements it issues one integer tensor-core instruction
+// (mma.sync m16n8k32, u8/s8 x s8 -> s32) whose 16 x 32 A operand is built in registers from the
+// packed nibbles / 6-bit fields with a couple of logic ops, and whose B operand is the digit
+// planes (one column per plane) read from shared memory. The exact integer sub-block sums are
+// multiplied by the integer sub-block scales (6-bit for Q4_K, int8 for Q6_K) with integer
+// multiply-adds; one float multiply per (row, 256-block) applies the fp16 block scale. The
+// Q4_K minimum term and the Q6_K "-32" offset use per-sub-block sums of the activations, also
+// kept as digit bytes, and are evaluated with dp4a. Rows are finished with warp shuffles.
 //
-// HBM traffic per launch = the packed bytes of the rows (each read once with 128-bit loads)
-// plus the activation vector; that is the kernel's algorithmic byte count.
+// Work split. One persistent CTA of 16 warps per SM takes a contiguous range of tiles; inside the
+// CTA the (tile, block) sequence is cut into 16 equal contiguous pieces, one per warp, so that
+// short matrices still keep every warp streaming. Partial row sums meet in shared memory in a
+// fixed order (deterministic).
+//
+// HBM traffic per launch = the packed bytes of the rows (each read exactly once, 64-bit and
+// 128-bit loads that bypass L1) plus the activation vector; that is the algorithmic byte count.
 #pragma once
 #include "common.cuh"
 #include "dequant.cuh"
@@ -17,6 +28,8 @@
 namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
+constexpr int GEMV_WARPS = 16;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 
 struct GemvSeg {
   const uint8_t* w;   // Q4_K: blocks as in the file; Q6_K: ql plane; Q8_0: qs plane
@@ -30,7 +43,7 @@ struct GemvSeg {
 struct GemvParams {
   GemvSeg seg[3];
   int nseg;
-  int K;                // input dimension (multiple of 256; of 64 for Q8_0-only launches)
+  int K;                // input dimension, a multiple of 256
   const float* x;       // [batch][x_stride]
   int x_stride;
   const float* norm_w;  // RMSNorm weight fused into the prologue, or nullptr
@@ -46,49 +59,59 @@ struct GemvParams {
   int max_pos;
   float* amax_val;      // optional per-CTA argmax partials [batch][gridDim.x]
   int* amax_idx;
+  int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
 };
 
 // ---- shared-memory activation image ------------------------------------------------------
-// Each plane stores 64-element chunks as four 16-byte pieces. Piece j of chunk c lives at
-//   ((c >> 5) * 4 + j) * 512 + slot(c & 31) * 16
-// so that a warp whose lanes read the same piece of 32 consecutive chunks (Q4_K, Q8_0), or of
-// every second chunk (Q6_K), touches every bank exactly once per quarter-warp.
-__host__ __device__ __forceinline__ int act_slot(int s) { return (s & 24) | ((s + ((s >> 3) & 1)) & 7); }
-__host__ __device__ __forceinline__ int act_plane_stride(int K) { return ((K / 64 + 31) / 32) * 2048; }
-__host__ __device__ __forceinline__ int act_sx_floats(int K) { return (K / 256 + 3) / 4 * 4; }  // keeps xs32/xs16 16-byte aligned
+// planes  [P][plane_stride]   digit bytes, element e of plane p at p*plane_stride + e; the stride
+//                             is = 32 (mod 128) so the planes read by one mma fall in distinct banks
+// sx      [K/256]             float scale of each 256-element block
+// xs32d   [4][K/32]           digit d of the sum of x_int over each 32 elements (Q4_K minimum term)
+// xs16d   [4][K/16]           the same per 16 elements (Q6_K offset term)
+__host__ __device__ __forceinline__ int act_plane_stride(int K) { return (K + 127) / 128 * 128 + 32; }
+__host__ __device__ __forceinline__ int act_sx_floats(int K) { return (K / 256 + 3) / 4 * 4; }
 __host__ __device__ __forceinline__ size_t act_smem_bytes(int K, int P) {
-  return (size_t)P * act_plane_stride(K) + (size_t)(act_sx_floats(K) + K / 32 + K / 16) * 4;
+  return (size_t)P * act_plane_stride(K) + (size_t)act_sx_floats(K) * 4 + (size_t)4 * (K / 32) + (size_t)4 * (K / 16);
 }
 
 struct ActImage {
   const uint8_t* planes;
   int plane_stride;
-  const float* sx;    // [K/256] scale of each 256-element block
-  const float* xs32;  // [K/32]  sum of the (quantised) activations per 32 elements
-  const float* xs16;  // [K/16]  per 16 elements
+  const float* sx;
+  const uint8_t* xs32d;
+  const uint8_t* xs16d;
+  int n32, n16;
 };
 
 __device__ __forceinline__ ActImage act_carve(uint8_t* smem, int K, int P) {
   ActImage a;
   a.plane_stride = act_plane_stride(K);
   a.planes = smem;
-  float* f = reinterpret_cast<float*>(smem + (size_t)P * a.plane_stride);
-  a.sx = f;
-  a.xs32 = f + act_sx_floats(K);
-  a.xs16 = a.xs32 + K / 32;
+  uint8_t* p = smem + (size_t)P * a.plane_stride;
+  a.sx = reinterpret_cast<const float*>(p);
+  p += act_sx_floats(K) * 4;
+  a.xs32d = p;
+  a.n32 = K / 32;
+  p += 4 * a.n32;
+  a.xs16d = p;
+  a.n16 = K / 16;
   return a;
 }
 
-__device__ __forceinline__ uint4 act_piece(const ActImage& a, int p, int chunk, int j) {
-  const uint8_t* ptr = a.planes + (size_t)p * a.plane_stride + ((chunk >> 5) * 4 + j) * 512 + act_slot(chunk & 31) * 16;
-  return *reinterpret_cast<const uint4*>(ptr);
+// balanced base-256 digits of v: v = d0 + 256 d1 + 65536 d2 + 2^24 d3, every d in [-128, 127]
+__device__ __forceinline__ void balanced_digits4(int v, int (&d)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    d[i] = (int)(int8_t)(v & 0xFF);
+    v = (v - d[i]) >> 8;
+  }
 }
 
 // Whole-CTA prologue: optional RMSNorm (reference utils.cpp:648-673: double mean of squares,
-// f = 1/sqrtf((float)mean + eps), out = x*f*w) then quantisation into the plane image.
+// f = 1/sqrtf((float)mean + eps), out = x*f*w) then quantisation into the image above.
 template <int P>
 __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
-                          int K, float* red /* 33 floats of shared scratch */) {
+                          int K, double* red /* 33 doubles of shared scratch */) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   float f = 1.0f;
   if (norm_w) {
@@ -100,27 +123,27 @@ __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const floa
     double ds = (double)ss;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
-    double* dred = reinterpret_cast<double*>(red);
-    if (lane == 0) dred[warp] = ds;
+    if (lane == 0) red[warp] = ds;
     __syncthreads();
     if (warp == 0) {
-      double t = lane < nwarps ? dred[lane] : 0.0;
+      double t = lane < nwarps ? red[lane] : 0.0;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
       if (lane == 0) {
         float mean = (float)(t / (double)K);
-        reinterpret_cast<float*>(dred + 32)[0] = 1.0f / sqrtf(mean + eps);
+        reinterpret_cast<float*>(red + 32)[0] = 1.0f / sqrtf(mean + eps);
       }
     }
     __syncthreads();
-    f = reinterpret_cast<float*>(dred + 32)[0];
+    f = reinterpret_cast<float*>(red + 32)[0];
   }
   ActImage a = act_carve(smem, K, P);
   uint8_t* planes = const_cast<uint8_t*>(a.planes);
   float* sx = const_cast<float*>(a.sx);
-  float* xs32 = const_cast<float*>(a.xs32);
-  float* xs16 = const_cast<float*>(a.xs16);
-  constexpr int QMAX = (1 << (8 * P - 1)) - 1;
+  uint8_t* xs32d = const_cast<uint8_t*>(a.xs32d);
+  uint8_t* xs16d = const_cast<uint8_t*>(a.xs16d);
+  // largest magnitude P balanced digits can hold: 127 * (256^P - 1) / 255
+  constexpr int QMAX = P == 3 ? 8355711 : (P == 2 ? 32639 : 127);
   const int nblk = K / 256;
   for (int b = warp; b < nblk; b += nwarps) {
     const int e0 = b * 256 + lane * 8;
@@ -138,48 +161,71 @@ __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const floa
     amax = warp_max(amax);
     const float scale = amax / (float)QMAX;
     const float inv = amax > 0.f ? (float)QMAX / amax : 0.f;
-    int xi[8];
     int s8 = 0;
+    uint32_t pw[P][2];
+#pragma unroll
+    for (int p = 0; p < P; ++p) pw[p][0] = pw[p][1] = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       int q = __float2int_rn(v[i] * inv);
       q = max(-QMAX, min(QMAX, q));
-      xi[i] = q;
       s8 += q;
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        const int dgt = (int)(int8_t)(q & 0xFF);
+        q = (q - dgt) >> 8;
+        pw[p][i >> 2] |= (uint32_t)(dgt & 0xFF) << (8 * (i & 3));
+      }
     }
+#pragma unroll
+    for (int p = 0; p < P; ++p)
+      *reinterpret_cast<uint2*>(planes + (size_t)p * a.plane_stride + e0) = make_uint2(pw[p][0], pw[p][1]);
     const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
     const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-    if ((lane & 1) == 0) xs16[b * 16 + (lane >> 1)] = scale * (float)s16;
-    if ((lane & 3) == 0) xs32[b * 8 + (lane >> 2)] = scale * (float)s32;
-    if (lane == 0) sx[b] = scale;
-    const int chunk = b * 4 + (lane >> 3), j = (lane & 7) >> 1, off8 = (lane & 1) * 8;
+    if ((lane & 1) == 0) {
+      int dg[4];
+      balanced_digits4(s16, dg);
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        w0 |= (uint32_t)((xi[i] >> (8 * p)) & 0xFF) << (8 * i);
-        w1 |= (uint32_t)((xi[4 + i] >> (8 * p)) & 0xFF) << (8 * i);
-      }
-      uint8_t* dst = planes + (size_t)p * a.plane_stride + ((chunk >> 5) * 4 + j) * 512 + act_slot(chunk & 31) * 16 + off8;
-      *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+      for (int i = 0; i < 4; ++i) xs16d[i * a.n16 + b * 16 + (lane >> 1)] = (uint8_t)dg[i];
     }
+    if ((lane & 3) == 0) {
+      int dg[4];
+      balanced_digits4(s32, dg);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xs32d[i * a.n32 + b * 8 + (lane >> 2)] = (uint8_t)dg[i];
+    }
+    if (lane == 0) sx[b] = scale;
   }
   __syncthreads();
 }
 
-template <int P>
-__device__ __forceinline__ float combine_planes(const int (&I)[P]) {
-  if (P == 1) return (float)I[0];
-  if (P == 2) return fmaf((float)I[1], 256.f, (float)I[0]);
-  return fmaf((float)I[P - 1], 65536.f, fmaf((float)I[1], 256.f, (float)I[0]));
+// D(16x8, s32) = A(16x32, u8 or s8) * B(32x8, s8); C = 0.
+template <bool A_SIGNED>
+__device__ __forceinline__ void imma_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (A_SIGNED)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// dot of four weight bytes with plane p of the activations; WS = weights signed
-template <int P, bool WS>
-__device__ __forceinline__ int dotp(int p, uint32_t w, uint32_t x, int c) {
-  if (p == P - 1) return WS ? dp4a_ss(w, x, c) : dp4a_us(w, x, c);
-  return WS ? dp4a_su(w, x, c) : dp4a_uu(w, x, c);
+__device__ __forceinline__ uint2 ldg64_stream(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+// byte i (0..3) of w, zero-extended / sign-extended (i is a compile-time constant after unrolling)
+__device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)__byte_perm(w, 0, 0x4440 | i); }
+__device__ __forceinline__ int byte_s(uint32_t w, uint32_t i) {
+  // prmt: a selector nibble with bit 3 set replicates the sign bit of the chosen byte
+  int d;
+  const uint32_t sel = i | ((8 | i) << 4) | ((8 | i) << 8) | ((8 | i) << 12);
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0), "r"(sel));
+  return d;
 }
 
 struct RowPtr {
@@ -188,203 +234,6 @@ struct RowPtr {
   const uint8_t* sc;
   const uint8_t* d;
 };
-
-// ---- Q4_K: one task = 64 weights = 32 bytes of nibbles (two complete sub-blocks) ----------
-template <int P, int NR>
-__device__ __forceinline__ void dot_q4k(const RowPtr (&rows)[NR], const ActImage& a, int K, int lane, float (&acc)[NR]) {
-  const int ntask = K / 64;
-  const int c = lane & 3;
-  for (int task = lane; task < ntask; task += 32) {
-    const int blk = task >> 2;
-    uint4 hdr[NR], qa[NR], qb[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const uint8_t* bp = rows[r].w + (size_t)blk * 144;
-      hdr[r] = ldg128(bp);
-      qa[r] = ldg128_stream(bp + 16 + 32 * c);
-      qb[r] = ldg128_stream(bp + 32 + 32 * c);
-    }
-    int Slo[NR][P], Shi[NR][P];
-#pragma unroll
-    for (int r = 0; r < NR; ++r)
-#pragma unroll
-      for (int p = 0; p < P; ++p) Slo[r][p] = Shi[r][p] = 0;
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const uint4 x0 = act_piece(a, p, task, 0), x1 = act_piece(a, p, task, 1);
-      const uint4 x2 = act_piece(a, p, task, 2), x3 = act_piece(a, p, task, 3);
-      const uint32_t xl[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-      const uint32_t xh[8] = {x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w};
-#pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const uint32_t q[8] = {qa[r].x, qa[r].y, qa[r].z, qa[r].w, qb[r].x, qb[r].y, qb[r].z, qb[r].w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          Slo[r][p] = dotp<P, false>(p, q[j] & 0x0F0F0F0Fu, xl[j], Slo[r][p]);
-          Shi[r][p] = dotp<P, false>(p, q[j] & 0xF0F0F0F0u, xh[j], Shi[r][p]);  // 16x the nibble sum
-        }
-      }
-    }
-    const float sxb = a.sx[blk];
-    const float xs_lo = a.xs32[2 * task], xs_hi = a.xs32[2 * task + 1];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const uint32_t yb = (hdr[r].y >> (8 * (c & 1) * 2)) , zb = (hdr[r].z >> (8 * (c & 1) * 2)), wb = (hdr[r].w >> (8 * (c & 1) * 2));
-      // sub-blocks j0 = 2c, j1 = 2c+1 -> byte indices (j & 3) = 2(c&1), 2(c&1)+1
-      const uint32_t y0 = yb & 0xFF, y1 = (yb >> 8) & 0xFF, z0 = zb & 0xFF, z1 = (zb >> 8) & 0xFF;
-      const uint32_t w0 = wb & 0xFF, w1 = (wb >> 8) & 0xFF;
-      int sc0, sc1, m0, m1;
-      if (c < 2) {
-        sc0 = y0 & 63; m0 = z0 & 63; sc1 = y1 & 63; m1 = z1 & 63;
-      } else {
-        sc0 = (w0 & 0xF) | ((y0 >> 6) << 4); m0 = (w0 >> 4) | ((z0 >> 6) << 4);
-        sc1 = (w1 & 0xF) | ((y1 >> 6) << 4); m1 = (w1 >> 4) | ((z1 >> 6) << 4);
-      }
-      int I[P];
-#pragma unroll
-      for (int p = 0; p < P; ++p) I[p] = sc0 * Slo[r][p] + sc1 * (Shi[r][p] >> 4);
-      const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr[r].x));
-      const float fsum = combine_planes<P>(I);
-      acc[r] = fmaf(dm.x * sxb, fsum, acc[r]);
-      acc[r] = fmaf(-dm.y, fmaf((float)m0, xs_lo, (float)m1 * xs_hi), acc[r]);
-    }
-  }
-}
-
-// ---- Q6_K: one task = half a block = 128 weights in eight 16-element sub-blocks ----------
-template <int P, int NR>
-__device__ __forceinline__ void dot_q6k(const RowPtr (&rows)[NR], const ActImage& a, int K, int lane, float (&acc)[NR]) {
-  const int ntask = K / 128;
-  for (int task = lane; task < ntask; task += 32) {
-    const int blk = task >> 1, h = task & 1;
-    uint4 ql[NR][4], qh[NR][2];
-    uint2 scw[NR];
-    uint16_t dh[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const uint8_t* pl = rows[r].w + (size_t)blk * 128 + 64 * h;
-      const uint8_t* ph = rows[r].qh + (size_t)blk * 64 + 32 * h;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) ql[r][i] = ldg128_stream(pl + 16 * i);
-      qh[r][0] = ldg128_stream(ph);
-      qh[r][1] = ldg128_stream(ph + 16);
-      scw[r] = ldg64(rows[r].sc + (size_t)blk * 16 + 8 * h);
-      dh[r] = ldg16(rows[r].d + (size_t)blk * 2);
-    }
-    int I[NR][P];
-#pragma unroll
-    for (int r = 0; r < NR; ++r)
-#pragma unroll
-      for (int p = 0; p < P; ++p) I[r][p] = 0;
-    // group g: 0 -> elements 0..31 (chunk A pieces 0,1), 1 -> 32..63 (A pieces 2,3),
-    //          2 -> 64..95 (chunk B pieces 0,1), 3 -> 96..127 (B pieces 2,3)
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-#pragma unroll
-      for (int is = 0; is < 2; ++is) {
-        uint32_t qv[NR][4];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const uint4 lw = ql[r][(g & 1) * 2 + is];  // ql bytes (g&1)*32 + 16*is ..
-          const uint4 hw = qh[r][is];                // qh bytes 16*is ..
-          const uint32_t l4[4] = {lw.x, lw.y, lw.z, lw.w}, h4[4] = {hw.x, hw.y, hw.z, hw.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t lo = (g < 2) ? (l4[j] & 0x0F0F0F0Fu) : ((l4[j] >> 4) & 0x0F0F0F0Fu);
-            uint32_t hb;
-            if (g == 0) hb = (h4[j] << 4);
-            else if (g == 1) hb = (h4[j] << 2);
-            else if (g == 2) hb = h4[j];
-            else hb = (h4[j] >> 2);
-            qv[r][j] = lo | (hb & 0x30303030u);
-          }
-        }
-        int S[NR][P];
-#pragma unroll
-        for (int p = 0; p < P; ++p) {
-          const uint4 xv = act_piece(a, p, 2 * task + (g >> 1), (g & 1) * 2 + is);
-          const uint32_t x4[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-          for (int r = 0; r < NR; ++r) {
-            int s = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s = dotp<P, false>(p, qv[r][j], x4[j], s);
-            S[r][p] = s;
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const int k = 2 * g + is;  // sub-scale index within the half
-          const uint32_t word = k < 4 ? scw[r].x : scw[r].y;
-          const int sc = (int)(int8_t)((word >> (8 * (k & 3))) & 0xFF);
-#pragma unroll
-          for (int p = 0; p < P; ++p) I[r][p] += sc * S[r][p];
-        }
-      }
-    }
-    const float sxb = a.sx[blk];
-    const float4 xa = *reinterpret_cast<const float4*>(a.xs16 + 8 * task);
-    const float4 xb = *reinterpret_cast<const float4*>(a.xs16 + 8 * task + 4);
-    const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      float corr = 0.f;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const uint32_t word = k < 4 ? scw[r].x : scw[r].y;
-        corr = fmaf((float)(int)(int8_t)((word >> (8 * (k & 3))) & 0xFF), xs[k], corr);
-      }
-      const float d = half_bits_to_float(dh[r]);
-      acc[r] = fmaf(d, fmaf(sxb, combine_planes<P>(I[r]), -32.f * corr), acc[r]);
-    }
-  }
-}
-
-// ---- Q8_0: one task = two blocks = 64 signed bytes -----------------------------------------
-template <int P, int NR>
-__device__ __forceinline__ void dot_q80(const RowPtr (&rows)[NR], const ActImage& a, int K, int lane, float (&acc)[NR]) {
-  const int ntask = K / 64;
-  for (int task = lane; task < ntask; task += 32) {
-    uint4 q[NR][4];
-    uint32_t dd[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const uint8_t* pq = rows[r].w + (size_t)task * 64;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) q[r][i] = ldg128_stream(pq + 16 * i);
-      dd[r] = ldg32(rows[r].d + (size_t)task * 4);
-    }
-    int I0[NR][P], I1[NR][P];
-#pragma unroll
-    for (int r = 0; r < NR; ++r)
-#pragma unroll
-      for (int p = 0; p < P; ++p) I0[r][p] = I1[r][p] = 0;
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 xv = act_piece(a, p, task, i);
-        const uint32_t x4[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const uint32_t w4[4] = {q[r][i].x, q[r][i].y, q[r][i].z, q[r][i].w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (i < 2) I0[r][p] = dotp<P, true>(p, w4[j], x4[j], I0[r][p]);
-            else I1[r][p] = dotp<P, true>(p, w4[j], x4[j], I1[r][p]);
-          }
-        }
-      }
-    }
-    const float sxb = a.sx[task >> 2];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-      const float d0 = scale_field_to_float((uint16_t)(dd[r] & 0xFFFF)), d1 = scale_field_to_float((uint16_t)(dd[r] >> 16));
-      acc[r] = fmaf(d0 * sxb, combine_planes<P>(I0[r]), acc[r]);
-      acc[r] = fmaf(d1 * sxb, combine_planes<P>(I1[r]), acc[r]);
-    }
-  }
-}
 
 __device__ __forceinline__ RowPtr row_ptr(const GemvSeg& s, int row, int K) {
   RowPtr r;
@@ -400,94 +249,376 @@ __device__ __forceinline__ RowPtr row_ptr(const GemvSeg& s, int row, int K) {
   return r;
 }
 
-// One CTA = 8 warps; blockIdx.y = batch element. Each warp walks over row pairs.
+// ---- per-format work on one 256-element block of a 16-row tile ----------------------------
+// Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the tile and the four k-slices
+// 8t .. 8t+7 of every 32-element group; it receives columns 2t and 2t+1 of the product.
+struct LaneCtx {
+  int g, t;
+  float wa, wb;  // 256^plane of columns 2t, 2t+1 (0 for unused columns)
+  float wd;      // 256^t: weight of digit t in the minimum / offset terms
+};
+
 template <int P>
-__global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams prm) {
-  extern __shared__ __align__(16) uint8_t smem[];
+__device__ __forceinline__ uint2 b_frag(const ActImage& a, int col, int elem) {
+  if (col < P) return *reinterpret_cast<const uint2*>(a.planes + (size_t)col * a.plane_stride + elem);
+  return make_uint2(0u, 0u);
+}
+
+struct RawQ4 {
+  uint2 q[2][4];
+  uint4 h[2];
+};
+__device__ __forceinline__ void load_q4(RawQ4& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
+  const uint8_t* pa = ra.w + (size_t)blk * 144;
+  const uint8_t* pb = rb.w + (size_t)blk * 144;
+  r.h[0] = ldg128_stream(pa);
+  r.h[1] = ldg128_stream(pb);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    r.q[0][c] = ldg64_stream(pa + 16 + 32 * c + 8 * t);
+    r.q[1][c] = ldg64_stream(pb + 16 + 32 * c + 8 * t);
+  }
+}
+
+template <int P>
+__device__ __forceinline__ void compute_q4(const RawQ4& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
+  // eight 6-bit scales and minima per row, four to a word (get_scale_min_k4 of the reference,
+  // quantization.cpp:145-155, applied to four sub-blocks at once)
+  uint32_t scA[2], scB[2], mnA[2], mnB[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t y = r.h[i].y, z = r.h[i].z, w = r.h[i].w;
+    scA[i] = y & 0x3F3F3F3Fu;
+    mnA[i] = z & 0x3F3F3F3Fu;
+    scB[i] = (w & 0x0F0F0F0Fu) | ((y >> 2) & 0x30303030u);
+    mnB[i] = ((w >> 4) & 0x0F0F0F0Fu) | ((z >> 2) & 0x30303030u);
+  }
+  int Jlo[4] = {0, 0, 0, 0}, Jhi[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int e = blk * 256 + 64 * c + 8 * L.t;
+    const uint2 bl = b_frag<P>(a, L.g, e), bh = b_frag<P>(a, L.g, e + 32);
+    int cl[4], ch[4];
+    imma_16x8x32<false>(cl, r.q[0][c].x & 0x0F0F0F0Fu, r.q[1][c].x & 0x0F0F0F0Fu, r.q[0][c].y & 0x0F0F0F0Fu,
+                        r.q[1][c].y & 0x0F0F0F0Fu, bl.x, bl.y);
+    imma_16x8x32<false>(ch, r.q[0][c].x & 0xF0F0F0F0u, r.q[1][c].x & 0xF0F0F0F0u, r.q[0][c].y & 0xF0F0F0F0u,
+                        r.q[1][c].y & 0xF0F0F0F0u, bh.x, bh.y);  // 16 x the high-nibble sums
+    const int sl0 = byte_u(c < 2 ? scA[0] : scB[0], (2 * c) & 3), sh0 = byte_u(c < 2 ? scA[0] : scB[0], (2 * c + 1) & 3);
+    const int sl1 = byte_u(c < 2 ? scA[1] : scB[1], (2 * c) & 3), sh1 = byte_u(c < 2 ? scA[1] : scB[1], (2 * c + 1) & 3);
+    Jlo[0] += sl0 * cl[0]; Jlo[1] += sl0 * cl[1]; Jlo[2] += sl1 * cl[2]; Jlo[3] += sl1 * cl[3];
+    Jhi[0] += sh0 * ch[0]; Jhi[1] += sh0 * ch[1]; Jhi[2] += sh1 * ch[2]; Jhi[3] += sh1 * ch[3];
+  }
+  const float f0 = L.wa * fmaf((float)Jhi[0], 0.0625f, (float)Jlo[0]) + L.wb * fmaf((float)Jhi[1], 0.0625f, (float)Jlo[1]);
+  const float f1 = L.wa * fmaf((float)Jhi[2], 0.0625f, (float)Jlo[2]) + L.wb * fmaf((float)Jhi[3], 0.0625f, (float)Jlo[3]);
+  // minimum term: sum_sub m_sub * X_sub, digit t of X handled by lane t
+  const uint2 xw = *reinterpret_cast<const uint2*>(a.xs32d + (size_t)L.t * a.n32 + blk * 8);
+  const int M0 = dp4a_us(mnB[0], xw.y, dp4a_us(mnA[0], xw.x, 0));
+  const int M1 = dp4a_us(mnB[1], xw.y, dp4a_us(mnA[1], xw.x, 0));
+  const float sxb = a.sx[blk];
+  const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&r.h[0].x));
+  const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&r.h[1].x));
+  acc0 = fmaf(sxb, dm0.x * f0 - dm0.y * (L.wd * (float)M0), acc0);
+  acc1 = fmaf(sxb, dm1.x * f1 - dm1.y * (L.wd * (float)M1), acc1);
+}
+
+struct RawQ6 {
+  uint2 ql[2][4];  // [row][half*2 + (low|high 32 bytes)]
+  uint2 qh[2][2];  // [row][half]
+  uint4 sc[2];
+  uint16_t d[2];
+};
+__device__ __forceinline__ void load_q6(RawQ6& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const RowPtr& rp = i ? rb : ra;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r.ql[i][j] = ldg64_stream(rp.w + (size_t)blk * 128 + 32 * j + 8 * t);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) r.qh[i][h] = ldg64_stream(rp.qh + (size_t)blk * 64 + 32 * h + 8 * t);
+    r.sc[i] = ldg128_stream(rp.sc + (size_t)blk * 16);
+    r.d[i] = ldg16(rp.d + (size_t)blk * 2);
+  }
+}
+
+// Q6_K: a group of 32 consecutive elements holds two 16-element sub-blocks. Lanes t = 0,1 carry
+// the first one, t = 2,3 the second; columns 0..P-1 see only the first (B is zero for t >= 2),
+// columns P..2P-1 only the second, so one instruction yields both sub-block sums separately.
+template <int P>
+__device__ __forceinline__ void compute_q6(const RawQ6& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
+  const int col = L.g, sub_of_col = col / P, plane = col - sub_of_col * P;
+  const bool b_on = col < 2 * P && sub_of_col == (L.t >> 1);
+  // which sub-block (0/1) columns 2t and 2t+1 belong to
+  const uint32_t selA = (uint32_t)((2 * L.t) / P), selB = (uint32_t)((2 * L.t + 1) / P);
+  int J[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t hf[2][2][4];  // [row][word][field] : 2-bit fields moved to bits 4-5 of every byte
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t hw[2] = {r.qh[i][h].x, r.qh[i][h].y};
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        hf[i][w][0] = (hw[w] << 4) & 0x30303030u;
+        hf[i][w][1] = (hw[w] << 2) & 0x30303030u;
+        hf[i][w][2] = hw[w] & 0x30303030u;
+        hf[i][w][3] = (hw[w] >> 2) & 0x30303030u;
+      }
+    }
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4) {
+      uint32_t av[2][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint2 lw = r.ql[i][h * 2 + (g4 & 1)];
+        const uint32_t l2[2] = {lw.x, lw.y};
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const uint32_t nib = g4 < 2 ? (l2[w] & 0x0F0F0F0Fu) : ((l2[w] >> 4) & 0x0F0F0F0Fu);
+          av[i][w] = nib | hf[i][w][g4];
+        }
+      }
+      const int e = blk * 256 + 128 * h + 32 * g4 + 8 * L.t;
+      uint2 bv = make_uint2(0u, 0u);
+      if (b_on) bv = *reinterpret_cast<const uint2*>(a.planes + (size_t)plane * a.plane_stride + e);
+      int c[4];
+      imma_16x8x32<false>(c, av[0][0], av[1][0], av[0][1], av[1][1], bv.x, bv.y);
+      // sub-scale index within the block: 8h + 2*g4 + (0|1) -> word (2h + g4/2), byte 2(g4&1) + sel
+      const int wsel = 2 * h + (g4 >> 1);
+      const uint32_t w0 = wsel == 0 ? r.sc[0].x : wsel == 1 ? r.sc[0].y : wsel == 2 ? r.sc[0].z : r.sc[0].w;
+      const uint32_t w1 = wsel == 0 ? r.sc[1].x : wsel == 1 ? r.sc[1].y : wsel == 2 ? r.sc[1].z : r.sc[1].w;
+      const uint32_t bA = 2 * (g4 & 1) + selA, bB = 2 * (g4 & 1) + selB;
+      J[0] += byte_s(w0, bA) * c[0];
+      J[1] += byte_s(w0, bB) * c[1];
+      J[2] += byte_s(w1, bA) * c[2];
+      J[3] += byte_s(w1, bB) * c[3];
+    }
+  }
+  const float f0 = L.wa * (float)J[0] + L.wb * (float)J[1];
+  const float f1 = L.wa * (float)J[2] + L.wb * (float)J[3];
+  // offset term: the stored quants are q + 32, so subtract 32 * sum_sub sc_sub * X_sub (digit t per lane)
+  const uint4 xw = *reinterpret_cast<const uint4*>(a.xs16d + (size_t)L.t * a.n16 + blk * 16);
+  const int C0 = dp4a_ss(r.sc[0].w, xw.w, dp4a_ss(r.sc[0].z, xw.z, dp4a_ss(r.sc[0].y, xw.y, dp4a_ss(r.sc[0].x, xw.x, 0))));
+  const int C1 = dp4a_ss(r.sc[1].w, xw.w, dp4a_ss(r.sc[1].z, xw.z, dp4a_ss(r.sc[1].y, xw.y, dp4a_ss(r.sc[1].x, xw.x, 0))));
+  const float sxb = a.sx[blk];
+  acc0 = fmaf(sxb * half_bits_to_float(r.d[0]), f0 - 32.f * (L.wd * (float)C0), acc0);
+  acc1 = fmaf(sxb * half_bits_to_float(r.d[1]), f1 - 32.f * (L.wd * (float)C1), acc1);
+}
+
+struct RawQ8 {
+  uint2 q[2][8];
+  uint4 d[2];
+};
+__device__ __forceinline__ void load_q8(RawQ8& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const RowPtr& rp = i ? rb : ra;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r.q[i][j] = ldg64_stream(rp.w + (size_t)blk * 256 + 32 * j + 8 * t);
+    r.d[i] = ldg128_stream(rp.d + (size_t)blk * 16);
+  }
+}
+
+template <int P>
+__device__ __forceinline__ void compute_q8(const RawQ8& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
+  const uint32_t dw0[4] = {r.d[0].x, r.d[0].y, r.d[0].z, r.d[0].w}, dw1[4] = {r.d[1].x, r.d[1].y, r.d[1].z, r.d[1].w};
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint2 bv = b_frag<P>(a, L.g, blk * 256 + 32 * j + 8 * L.t);
+    int c[4];
+    imma_16x8x32<true>(c, r.q[0][j].x, r.q[1][j].x, r.q[0][j].y, r.q[1][j].y, bv.x, bv.y);
+    // the scale field of a Q8_0 block is used by magnitude (reference quantization.cpp:85-87)
+    const float d0 = scale_field_to_float((uint16_t)((dw0[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
+    const float d1 = scale_field_to_float((uint16_t)((dw1[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
+    s0 = fmaf(d0, L.wa * (float)c[0] + L.wb * (float)c[1], s0);
+    s1 = fmaf(d1, L.wa * (float)c[2] + L.wb * (float)c[3], s1);
+  }
+  const float sxb = a.sx[blk];
+  acc0 = fmaf(sxb, s0, acc0);
+  acc1 = fmaf(sxb, s1, acc1);
+}
+
+// blocks [blk0, blk1) of one tile for this warp; the next block's loads are in flight while the
+// current one is multiplied (two register buffers used alternately)
+#define B200_SEGMENT_LOOP(RAW, LOAD, COMPUTE)                   \
+  {                                                             \
+    RAW bufA, bufB;                                             \
+    LOAD(bufA, ra, rb, blk0, L.t);                              \
+    int b = blk0;                                               \
+    while (true) {                                              \
+      if (b + 1 < blk1) LOAD(bufB, ra, rb, b + 1, L.t);         \
+      COMPUTE<P>(bufA, a, b, L, acc0, acc1);                    \
+      if (++b >= blk1) break;                                   \
+      if (b + 1 < blk1) LOAD(bufA, ra, rb, b + 1, L.t);         \
+      COMPUTE<P>(bufB, a, b, L, acc0, acc1);                    \
+      if (++b >= blk1) break;                                   \
+    }                                                           \
+  }
+
+template <int P>
+__device__ __forceinline__ void tile_segment(int type, const RowPtr& ra, const RowPtr& rb, const ActImage& a, int blk0, int blk1,
+                                             LaneCtx L, float wa6, float wb6, float& acc0, float& acc1) {
+  if (type == T_Q4_K) {
+    B200_SEGMENT_LOOP(RawQ4, load_q4, compute_q4)
+  } else if (type == T_Q6_K) {
+    L.wa = wa6;
+    L.wb = wb6;
+    B200_SEGMENT_LOOP(RawQ6, load_q6, compute_q6)
+  } else {
+    B200_SEGMENT_LOOP(RawQ8, load_q8, compute_q8)
+  }
+}
+
+// Maps (tile, row-in-tile 0..15) to a segment and a row of it. Ordinary launches: the segments'
+// rows are concatenated and cut into 16-row tiles (every segment but the last has a multiple of
+// 16 rows). SwiGLU launches: tile = 8 rows of seg 0 (gate) followed by the same 8 rows of seg 1 (up).
+__device__ __forceinline__ void tile_row(const GemvParams& p, int tile, int r, int& seg, int& row, bool& valid) {
+  if (p.epi == EPI_SWIGLU) {
+    seg = r >> 3;
+    row = tile * 8 + (r & 7);
+    valid = row < p.seg[0].rows;
+  } else {
+    row = tile * 16 + r;
+    seg = 0;
+    while (seg + 1 < p.nseg && row >= p.seg[seg].rows) { row -= p.seg[seg].rows; ++seg; }
+    valid = row < p.seg[seg].rows;
+  }
+  if (!valid) row = p.seg[seg].rows - 1;  // loads stay in bounds; the result is discarded
+}
+
+template <int P>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm) {
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ double red_scratch[34];
-  const int b = blockIdx.y;
+  __shared__ float part[GEMV_WARPS][2][16];
+  __shared__ int part_tile[GEMV_WARPS][2];
+  __shared__ float sv[GEMV_WARPS];
+  __shared__ int si[GEMV_WARPS];
+  const int bidx = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  act_build<P>(smem, prm.x + (size_t)b * prm.x_stride, prm.norm_w, prm.eps, prm.K, reinterpret_cast<float*>(red_scratch));
+  act_build<P>(smem, prm.x + (size_t)bidx * prm.x_stride, prm.norm_w, prm.eps, prm.K, red_scratch);
   const ActImage a = act_carve(smem, prm.K, P);
 
-  int total_rows = 0;
-  for (int s = 0; s < prm.nseg; ++s) total_rows += prm.seg[s].rows;
-  const int npairs = prm.epi == EPI_SWIGLU ? prm.seg[0].rows : total_rows / 2;
-  const int wpc = blockDim.x >> 5;
+  LaneCtx L;
+  L.g = lane >> 2;
+  L.t = lane & 3;
+  const float pw[4] = {1.f, 256.f, 65536.f, 16777216.f};
+  {
+    const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
+    L.wa = c0 < P ? pw[c0] : 0.f;
+    L.wb = c1 < P ? pw[c1] : 0.f;
+    L.wd = pw[L.t];
+  }
+  float wa6, wb6;
+  {
+    const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
+    wa6 = c0 < 2 * P ? pw[c0 % P] : 0.f;
+    wb6 = c1 < 2 * P ? pw[c1 % P] : 0.f;
+  }
+
+  const int nblk = prm.K / 256;
+  const int tA = (int)((long long)blockIdx.x * prm.ntiles / gridDim.x);
+  const int tB = (int)((long long)(blockIdx.x + 1) * prm.ntiles / gridDim.x);
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
 
-  for (int pair = blockIdx.x * wpc + warp; pair < npairs; pair += gridDim.x * wpc) {
-    RowPtr rows[2];
-    int type, seg_id = 0, row0;
-    if (prm.epi == EPI_SWIGLU) {
-      rows[0] = row_ptr(prm.seg[0], pair, prm.K);
-      rows[1] = row_ptr(prm.seg[1], pair, prm.K);
-      type = prm.seg[0].type;
-      row0 = pair;
-    } else {
-      row0 = 2 * pair;
-      while (seg_id + 1 < prm.nseg && row0 >= prm.seg[seg_id].rows) { row0 -= prm.seg[seg_id].rows; ++seg_id; }
-      rows[0] = row_ptr(prm.seg[seg_id], row0, prm.K);
-      rows[1] = row_ptr(prm.seg[seg_id], row0 + 1, prm.K);
-      type = prm.seg[seg_id].type;
+  for (int tb = tA; tb < tB; tb += GEMV_WARPS) {
+    const int nt = min(GEMV_WARPS, tB - tb);
+    const int total = nt * nblk;
+    const int i0 = (int)((long long)warp * total / GEMV_WARPS), i1 = (int)((long long)(warp + 1) * total / GEMV_WARPS);
+    int nseg_used = 0;
+    for (int i = i0; i < i1;) {
+      const int tl = i / nblk, blk0 = i - tl * nblk;
+      const int blk1 = min(nblk, blk0 + (i1 - i));
+      int segA, rowA, segB, rowB;
+      bool vA, vB;
+      tile_row(prm, tb + tl, L.g, segA, rowA, vA);
+      tile_row(prm, tb + tl, L.g + 8, segB, rowB, vB);
+      const RowPtr ra = row_ptr(prm.seg[segA], rowA, prm.K), rb = row_ptr(prm.seg[segB], rowB, prm.K);
+      float acc0 = 0.f, acc1 = 0.f;
+      tile_segment<P>(prm.seg[segA].type, ra, rb, a, blk0, blk1, L, wa6, wb6, acc0, acc1);
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+      if (nseg_used < 2) {
+        if (L.t == 0) {
+          part[warp][nseg_used][L.g] = acc0;
+          part[warp][nseg_used][L.g + 8] = acc1;
+        }
+        if (lane == 0) part_tile[warp][nseg_used] = tl;
+      }
+      ++nseg_used;
+      i += blk1 - blk0;
     }
-    float acc[2] = {0.f, 0.f};
-    if (type == T_Q4_K) dot_q4k<P, 2>(rows, a, prm.K, lane, acc);
-    else if (type == T_Q6_K) dot_q6k<P, 2>(rows, a, prm.K, lane, acc);
-    else dot_q80<P, 2>(rows, a, prm.K, lane, acc);
-    acc[0] = warp_sum(acc[0]);
-    acc[1] = warp_sum(acc[1]);
-    if (lane == 0) {
+    if (lane == 0)
+      for (int s = nseg_used; s < 2; ++s) part_tile[warp][s] = -1;
+    __syncthreads();
+
+    if (warp < nt) {  // warp j finishes tile j of this batch: lanes 0..15 own one row each
+      const int r = lane & 15;
+      float tot = 0.f;
+      for (int w = 0; w < GEMV_WARPS; ++w)
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+          if (part_tile[w][s] == warp) tot += part[w][s][r];
+      const int tile = tb + warp;
       if (prm.epi == EPI_SWIGLU) {
         // reference model.cpp:734-735 with silu_cpu (utils.cpp:700-707): (g * 1/(1+exp(-g))) * u
-        const float g = acc[0], u = acc[1];
-        const float sig = 1.0f / (1.0f + expf(-g));
-        prm.y[(size_t)b * prm.y_stride + row0] = (g * sig) * u;
-      } else if (prm.epi == EPI_RESID) {
-        float* y = prm.y + (size_t)b * prm.y_stride + row0;
-        y[0] = y[0] + acc[0];
-        y[1] = y[1] + acc[1];
-      } else if (prm.epi == EPI_QKV_ROPE) {
-        float v0 = acc[0], v1 = acc[1];
-        if (seg_id < 2) {  // q and k are rotated in adjacent pairs (reference utils.cpp:428-489)
-          const int pos = prm.positions[b];
-          if (pos >= 0 && pos < prm.max_pos) {
-            const int i = (row0 % prm.head_dim) >> 1;
-            const float2 cs = *reinterpret_cast<const float2*>(prm.rope + ((size_t)pos * (prm.head_dim >> 1) + i) * 2);
-            const float r0 = __fsub_rn(__fmul_rn(v0, cs.x), __fmul_rn(v1, cs.y));
-            const float r1 = __fadd_rn(__fmul_rn(v0, cs.y), __fmul_rn(v1, cs.x));
-            v0 = r0; v1 = r1;
-          }
+        const float u = __shfl_sync(0xffffffffu, tot, (lane & 7) + 8);
+        const int row = tile * 8 + (lane & 7);
+        if (lane < 8 && row < prm.seg[0].rows) {
+          const float sig = 1.0f / (1.0f + expf(-tot));
+          prm.y[(size_t)bidx * prm.y_stride + row] = (tot * sig) * u;
         }
-        float* dst = seg_id == 0 ? prm.y + (size_t)b * prm.y_stride + row0
-                                 : prm.y2 + (size_t)b * prm.y2_stride + (seg_id == 2 ? prm.seg[1].rows : 0) + row0;
-        dst[0] = v0;
-        dst[1] = v1;
       } else {
-        const int row = 2 * pair;
-        float* y = prm.y + (size_t)b * prm.y_stride + row;
-        y[0] = acc[0];
-        y[1] = acc[1];
-        if (prm.amax_val) {
-          if (acc[0] > best_v || (acc[0] == best_v && row < best_i)) { best_v = acc[0]; best_i = row; }
-          if (acc[1] > best_v || (acc[1] == best_v && row + 1 < best_i)) { best_v = acc[1]; best_i = row + 1; }
+        int seg, row;
+        bool valid;
+        tile_row(prm, tile, r, seg, row, valid);
+        const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
+        if (lane < 16 && valid) {
+          if (prm.epi == EPI_RESID) {
+            float* y = prm.y + (size_t)bidx * prm.y_stride + row;
+            *y = *y + tot;
+          } else if (prm.epi == EPI_QKV_ROPE) {
+            float v = tot;
+            if (seg < 2) {  // q and k are rotated in adjacent pairs (reference utils.cpp:428-489)
+              const int pos = prm.positions[bidx];
+              if (pos >= 0 && pos < prm.max_pos) {
+                const int i = (row % prm.head_dim) >> 1;
+                const float2 cs = *reinterpret_cast<const float2*>(prm.rope + ((size_t)pos * (prm.head_dim >> 1) + i) * 2);
+                v = (row & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(tot, cs.x))
+                              : __fsub_rn(__fmul_rn(tot, cs.x), __fmul_rn(other, cs.y));
+              }
+            }
+            float* dst = seg == 0 ? prm.y + (size_t)bidx * prm.y_stride + row
+                                  : prm.y2 + (size_t)bidx * prm.y2_stride + (seg == 2 ? prm.seg[1].rows : 0) + row;
+            *dst = v;
+          } else {
+            prm.y[(size_t)bidx * prm.y_stride + row] = tot;
+            if (tot > best_v || (tot == best_v && row < best_i)) { best_v = tot; best_i = row; }
+          }
         }
       }
     }
+    __syncthreads();
   }
   if (prm.amax_val) {  // per-CTA (value, first index) of the rows this CTA produced
-    __shared__ float sv[8];
-    __shared__ int si[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+    }
     if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
     __syncthreads();
     if (threadIdx.x == 0) {
       float bv = sv[0];
       int bi = si[0];
-      for (int w = 1; w < wpc; ++w)
+      for (int w = 1; w < GEMV_WARPS; ++w)
         if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-      prm.amax_val[(size_t)b * gridDim.x + blockIdx.x] = bv;
-      prm.amax_idx[(size_t)b * gridDim.x + blockIdx.x] = bi;
+      prm.amax_val[(size_t)bidx * gridDim.x + blockIdx.x] = bv;
+      prm.amax_idx[(size_t)bidx * gridDim.x + blockIdx.x] = bi;
     }
   }
 }
