@@ -45,6 +45,9 @@ __device__ __forceinline__ float i8_at(uint32_t w, int i) { return (float)(int)(
 template <bool KV_I8>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) {
   extern __shared__ __align__(16) float sm[];
+  // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
+  // it still waits for this grid to finish before touching anything produced here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int hd = prm.hd, G = prm.nq / prm.nkv, kvh = h / G;

@@ -67,34 +67,31 @@ __global__ void dequant_q6_k_kernel(const uint8_t* __restrict__ blocks, size_t n
   out[i] = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
 }
 
-// ---- load-time plane split -------------------------------------------------------------
-// A Q6_K block is 210 bytes and a Q8_0 block 34 bytes, so inside a row neither the quants nor
-// the scales of a block can sit on a 16-byte boundary, which 128-bit loads need. On the device
-// the same bytes are therefore kept as separate planes, each 16-byte aligned:
-//   Q6_K: ql [n][128] | qh [n][64] | scales [n][16] | d [n] (fp16)        (n = blocks in tensor)
-//   Q8_0: qs [n][32]  | d [n] (fp16)
+// ---- load-time regrouping ---------------------------------------------------------------
+// A Q6_K block is 210 bytes and a Q8_0 block 34 bytes, so in a row of them nothing sits on the
+// 16-byte boundaries that bulk copies and 128-bit loads need. On the device the same bytes are
+// therefore kept as 16-byte-aligned units of 256 elements (see gemv_unit_bytes):
+//   Q6_K: unit = first 208 bytes of the block (ql | qh | scales); the trailing fp16 d of every
+//         block goes to a separate plane d[block]
+//   Q8_0: unit = 272 bytes = the 32 quants of 8 consecutive blocks, then their 8 fp16 d
 // The byte count is unchanged (210 / 34 per block); nothing is expanded. Q4_K blocks are
 // 144 = 9 x 16 bytes and stay exactly as in the file.
-__global__ void split_q6_k_kernel(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ dst) {
+__global__ void split_q6_k_kernel(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ units,
+                                  uint8_t* __restrict__ dplane) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_blocks * 210) return;
   size_t blk = i / 210;
   int o = (int)(i % 210);
-  size_t di;
-  if (o < 128) di = blk * 128 + o;
-  else if (o < 192) di = n_blocks * 128 + blk * 64 + (o - 128);
-  else if (o < 208) di = n_blocks * 192 + blk * 16 + (o - 192);
-  else di = n_blocks * 208 + blk * 2 + (o - 208);
-  dst[di] = src[i];
+  if (o < 208) units[blk * 208 + o] = src[i];
+  else dplane[blk * 2 + (o - 208)] = src[i];
 }
 
-__global__ void split_q8_0_kernel(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ dst) {
+__global__ void regroup_q8_0_kernel(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ units) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_blocks * 34) return;
-  size_t blk = i / 34;
-  int o = (int)(i % 34);
-  size_t di = o >= 2 ? blk * 32 + (o - 2) : n_blocks * 32 + blk * 2 + o;
-  dst[di] = src[i];
+  size_t blk = i / 34, grp = blk / 8;
+  int j = (int)(blk % 8), o = (int)(i % 34);
+  units[grp * 272 + (o < 2 ? 256 + 2 * j + o : 32 * j + (o - 2))] = src[i];
 }
 
 }  // namespace b200

@@ -27,7 +27,7 @@ static T* dev_alloc(b200_engine* e, size_t n) {
 static void set_gemv_attrs() {
   static bool done = false;
   if (done) return;
-  const int maxb = 200 * 1024;
+  const int maxb = 208 * 1024;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -35,11 +35,11 @@ static void set_gemv_attrs() {
   done = true;
 }
 
-// Uploads one packed tensor; Q6_K / Q8_0 are split into aligned planes on the device.
+// Uploads one packed tensor and regroups Q6_K / Q8_0 into aligned 256-element units on the device.
 static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* host, size_t bytes, int64_t rows, int64_t cols,
                           cudaStream_t stream) {
   const int64_t be = type_block_elems(type), bb = type_block_bytes(type);
-  if (cols % be) throw std::runtime_error("tensor columns not a multiple of the block size");
+  if (cols % 256) throw std::runtime_error("tensor columns must be a multiple of 256");
   const size_t nblk = (size_t)(rows * cols / be);
   if (bytes != nblk * (size_t)bb) throw std::runtime_error("tensor byte count does not match rows x cols for its type");
   t.type = type; t.rows = rows; t.cols = cols; t.bytes = bytes;
@@ -48,14 +48,12 @@ static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* ho
     uint8_t* stage = nullptr;
     CK(cudaMalloc((void**)&stage, bytes));
     CK(cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, stream));
-    const size_t nthreads = bytes;
-    const unsigned grid = (unsigned)((nthreads + 255) / 256);
+    const unsigned grid = (unsigned)((bytes + 255) / 256);
     if (type == T_Q6_K) {
-      split_q6_k_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
-      t.qh = t.base + nblk * 128; t.sc = t.base + nblk * 192; t.d = t.base + nblk * 208;
+      t.d = t.base + (nblk * 208 + 15) / 16 * 16;
+      split_q6_k_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base, t.d);
     } else {
-      split_q8_0_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
-      t.d = t.base + nblk * 32;
+      regroup_q8_0_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
     }
     CK(cudaGetLastError());
     CK(cudaStreamSynchronize(stream));
@@ -68,14 +66,17 @@ static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* ho
 
 static GemvSeg seg_of(const DevTensor& t) {
   GemvSeg s;
-  s.w = t.base; s.qh = t.qh; s.sc = t.sc; s.d = t.d; s.type = t.type; s.rows = (int)t.rows;
+  s.w = t.base; s.d = t.d; s.type = t.type; s.rows = (int)t.rows;
   return s;
 }
 
-// Fills in the tile count, checks the launch's shape rules and starts the kernel with one
-// persistent CTA per SM (fewer when there are fewer tiles). Returns the grid width.
+// Fills in the tile count and ring geometry, checks the launch's shape rules and starts the
+// kernel with one persistent CTA per SM (fewer when there are fewer tiles), as a programmatic
+// dependent launch when the engine allows it. Returns the grid width.
 static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream_t st) {
   if (p.K % 256) throw std::runtime_error("gemv: K must be a multiple of 256");
+  int max_ub = 0;
+  for (int s = 0; s < p.nseg; ++s) max_ub = std::max(max_ub, gemv_unit_bytes(p.seg[s].type));
   if (p.epi == EPI_SWIGLU) {
     if (p.nseg != 2 || p.seg[0].rows != p.seg[1].rows || p.seg[0].type != p.seg[1].type)
       throw std::runtime_error("gemv: gate and up must have the same shape and block type");
@@ -88,13 +89,27 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
     }
     p.ntiles = (rows + 15) / 16;
   }
-  const size_t smem = act_smem_bytes(p.K, e->P);
-  if (smem > 200 * 1024) throw std::runtime_error("gemv: input dimension too large for the shared-memory activation image");
+  const int nblk = p.K / 256;
+  p.row_stride = (std::min(nblk, GEMV_SLAB) * max_ub + 127) / 128 * 128 + 32;
+  const size_t ring_off = gemv_ring_offset(p.K, e->P), stage = (size_t)16 * p.row_stride;
+  const size_t budget = 200 * 1024;
+  if (ring_off + 2 * stage > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
+  p.nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / stage);
+  p.error_flag = e->d_error;
+  const size_t smem = ring_off + p.nstages * stage;
   const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
-  dim3 grid(gx, batch);
-  if (e->P == 2) gemv_kernel<2><<<grid, GEMV_THREADS, smem, st>>>(p);
-  else gemv_kernel<3><<<grid, GEMV_THREADS, smem, st>>>(p);
-  CK(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(gx, batch);
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = e->use_pdl ? 1 : 0;
+  if (e->P == 2) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2>, p));
+  else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3>, p));
   return gx;
 }
 

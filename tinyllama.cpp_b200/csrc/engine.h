@@ -13,10 +13,8 @@ namespace b200 {
 struct DevTensor {
   int type = -1;
   int64_t rows = 0, cols = 0;
-  uint8_t* base = nullptr;  // Q4_K blocks / Q6_K ql plane / Q8_0 qs plane / F32 data
-  uint8_t* qh = nullptr;
-  uint8_t* sc = nullptr;
-  uint8_t* d = nullptr;
+  uint8_t* base = nullptr;  // 256-element units (see gemv_unit_bytes) or F32 data
+  uint8_t* d = nullptr;     // Q6_K: fp16 block scales [rows][K/256]
   size_t bytes = 0;
   bool present() const { return base != nullptr; }
   const float* f32() const { return reinterpret_cast<const float*>(base); }
@@ -43,6 +41,8 @@ struct b200_engine {
   b200_model_desc desc{};
   int H = 0, F = 0, nq = 0, nkv = 0, L = 0, V = 0, hd = 0, KVD = 0, max_ctx = 0, max_seqs = 0, P = 3;
   int num_sms = 148;
+  bool use_pdl = true;
+  int* d_error = nullptr;
   bool finalized = false;
   cudaStream_t stream = nullptr;
   std::vector<b200::LayerW> layers;

@@ -14,13 +14,19 @@
 // Q4_K minimum term and the Q6_K "-32" offset use per-sub-block sums of the activations, also
 // kept as digit bytes, and are evaluated with dp4a. Rows are finished with warp shuffles.
 //
-// Work split. One persistent CTA of 16 warps per SM takes a contiguous range of tiles; inside the
-// CTA the (tile, block) sequence is cut into 16 equal contiguous pieces, one per warp, so that
-// short matrices still keep every warp streaming. Partial row sums meet in shared memory in a
-// fixed order (deterministic).
+// Data movement. One persistent CTA per SM takes a contiguous range of 16-row tiles. A producer
+// warp streams every tile into a ring of shared-memory stages with bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier): one copy per row of up to 16 consecutive blocks, so
+// HBM sees long contiguous runs (a whole 16-row tile of a 4096-wide Q4_K matrix is 36 KB of
+// consecutive addresses) and several stages are in flight without holding registers. The 16
+// consumer warps each take one 256-element block column of the staged tile, build their mma
+// operands from shared memory, and their partial row sums meet in a fixed order (deterministic).
+// The first stages are requested before the activation prologue runs, and the kernel supports
+// programmatic dependent launch: weights are prefetched while the previous kernel drains, and
+// only then does it wait for that kernel's results.
 //
-// HBM traffic per launch = the packed bytes of the rows (each read exactly once, 64-bit and
-// 128-bit loads that bypass L1) plus the activation vector; that is the algorithmic byte count.
+// HBM traffic per launch = the packed bytes of the rows (each read exactly once) plus the
+// activation vector; that is the algorithmic byte count.
 #pragma once
 #include "common.cuh"
 #include "dequant.cuh"
@@ -28,14 +34,22 @@
 namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
-constexpr int GEMV_WARPS = 16;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_WARPS = 16;                       // consumer warps; one more warp produces
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;
+constexpr int GEMV_SLAB = 16;                        // 256-element blocks per row per stage
+constexpr int GEMV_MAX_STAGES = 4;
+
+// Device-resident form of a weight matrix, row-major, one "unit" per 256 elements of a row:
+//   Q4_K  unit = the 144-byte block exactly as in the file
+//   Q6_K  unit = 208 bytes: ql[128] | qh[64] | scales[16] of the block; the block's fp16 d lives
+//         in a separate plane d[row][block] (a 210-byte block cannot sit on a 16-byte boundary)
+//   Q8_0  unit = 272 bytes: the 8 x 32 quants of eight consecutive blocks, then their 8 fp16 d
+// The byte count is that of the file in every case; nothing is expanded.
+__host__ __device__ __forceinline__ int gemv_unit_bytes(int type) { return type == T_Q4_K ? 144 : type == T_Q6_K ? 208 : 272; }
 
 struct GemvSeg {
-  const uint8_t* w;   // Q4_K: blocks as in the file; Q6_K: ql plane; Q8_0: qs plane
-  const uint8_t* qh;  // Q6_K high-bit plane
-  const uint8_t* sc;  // Q6_K sub-scale plane
-  const uint8_t* d;   // Q6_K / Q8_0 fp16 scale plane
+  const uint8_t* w;  // units, [rows][K/256][unit]
+  const uint8_t* d;  // Q6_K only: fp16 [rows][K/256]
   int type;
   int rows;
 };
@@ -60,6 +74,9 @@ struct GemvParams {
   float* amax_val;      // optional per-CTA argmax partials [batch][gridDim.x]
   int* amax_idx;
   int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
+  int nstages;          // ring depth
+  int row_stride;       // bytes between rows of a stage in shared memory (= 32 mod 128)
+  int* error_flag;      // set when a bounded wait gives up
 };
 
 // ---- shared-memory activation image ------------------------------------------------------
@@ -98,6 +115,8 @@ __device__ __forceinline__ ActImage act_carve(uint8_t* smem, int K, int P) {
   return a;
 }
 
+__device__ __forceinline__ void consumer_sync();
+
 // balanced base-256 digits of v: v = d0 + 256 d1 + 65536 d2 + 2^24 d3, every d in [-128, 127]
 __device__ __forceinline__ void balanced_digits4(int v, int (&d)[4]) {
 #pragma unroll
@@ -112,11 +131,11 @@ __device__ __forceinline__ void balanced_digits4(int v, int (&d)[4]) {
 template <int P>
 __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
                           int K, double* red /* 33 doubles of shared scratch */) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = GEMV_WARPS;  // consumer warps only
   float f = 1.0f;
   if (norm_w) {
     float ss = 0.f;
-    for (int i = tid * 4; i < K; i += blockDim.x * 4) {
+    for (int i = tid * 4; i < K; i += GEMV_WARPS * 32 * 4) {
       float4 v = *reinterpret_cast<const float4*>(x + i);
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
@@ -124,7 +143,7 @@ __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const floa
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
     if (lane == 0) red[warp] = ds;
-    __syncthreads();
+    consumer_sync();
     if (warp == 0) {
       double t = lane < nwarps ? red[lane] : 0.0;
 #pragma unroll
@@ -134,7 +153,7 @@ __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const floa
         reinterpret_cast<float*>(red + 32)[0] = 1.0f / sqrtf(mean + eps);
       }
     }
-    __syncthreads();
+    consumer_sync();
     f = reinterpret_cast<float*>(red + 32)[0];
   }
   ActImage a = act_carve(smem, K, P);
@@ -196,7 +215,7 @@ __device__ void act_build(uint8_t* smem, const float* __restrict__ x, const floa
     }
     if (lane == 0) sx[b] = scale;
   }
-  __syncthreads();
+  consumer_sync();
 }
 
 // D(16x8, s32) = A(16x32, u8 or s8) * B(32x8, s8); C = 0.
@@ -228,83 +247,81 @@ __device__ __forceinline__ int byte_s(uint32_t w, uint32_t i) {
   return d;
 }
 
-struct RowPtr {
-  const uint8_t* w;
-  const uint8_t* qh;
-  const uint8_t* sc;
-  const uint8_t* d;
-};
 
-__device__ __forceinline__ RowPtr row_ptr(const GemvSeg& s, int row, int K) {
-  RowPtr r;
-  const size_t nb = (size_t)(K / (s.type == T_Q8_0 ? 32 : 256));
-  const size_t b0 = (size_t)row * nb;
-  if (s.type == T_Q4_K) {
-    r.w = s.w + b0 * 144; r.qh = r.sc = r.d = nullptr;
-  } else if (s.type == T_Q6_K) {
-    r.w = s.w + b0 * 128; r.qh = s.qh + b0 * 64; r.sc = s.sc + b0 * 16; r.d = s.d + b0 * 2;
-  } else {
-    r.w = s.w + b0 * 32; r.d = s.d + b0 * 2; r.qh = r.sc = nullptr;
-  }
-  return r;
+// ---- mbarrier / bulk-copy / launch-dependency primitives -----------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: gives up after a fixed number of probes and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < (1 << 20); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// global -> shared bulk copy (16-byte aligned addresses, size a multiple of 16); completion is
+// signalled on the mbarrier as transferred bytes
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); }
 
-// ---- per-format work on one 256-element block of a 16-row tile ----------------------------
-// Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the tile and the four k-slices
+// ---- per-format work on one 256-element block of a staged 16-row tile ----------------------
+// Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the tile and the k-slice
 // 8t .. 8t+7 of every 32-element group; it receives columns 2t and 2t+1 of the product.
+// pa / pb point at this block's unit in rows g / g + 8 of the stage; L.bplane already includes the lane's 8t offset.
 struct LaneCtx {
   int g, t;
-  float wa, wb;  // 256^plane of columns 2t, 2t+1 (0 for unused columns)
-  float wd;      // 256^t: weight of digit t in the minimum / offset terms
+  float wa, wb;    // 256^plane of columns 2t, 2t+1 for Q4_K / Q8_0 (0 for unused columns)
+  float wa6, wb6;  // the same for the Q6_K column layout
+  float wd;        // 256^t: weight of digit t in the minimum / offset terms
+  const uint8_t* bplane;  // digit plane this lane's B column reads (any valid plane for unused columns)
 };
 
 template <int P>
-__device__ __forceinline__ uint2 b_frag(const ActImage& a, int col, int elem) {
-  if (col < P) return *reinterpret_cast<const uint2*>(a.planes + (size_t)col * a.plane_stride + elem);
-  return make_uint2(0u, 0u);
-}
-
-struct RawQ4 {
-  uint2 q[2][4];
-  uint4 h[2];
-};
-__device__ __forceinline__ void load_q4(RawQ4& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
-  const uint8_t* pa = ra.w + (size_t)blk * 144;
-  const uint8_t* pb = rb.w + (size_t)blk * 144;
-  r.h[0] = ldg128_stream(pa);
-  r.h[1] = ldg128_stream(pb);
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    r.q[0][c] = ldg64_stream(pa + 16 + 32 * c + 8 * t);
-    r.q[1][c] = ldg64_stream(pb + 16 + 32 * c + 8 * t);
-  }
-}
-
-template <int P>
-__device__ __forceinline__ void compute_q4(const RawQ4& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
+__device__ __forceinline__ void compute_q4(const uint8_t* pa, const uint8_t* pb, const ActImage& a, int blk, const LaneCtx& L,
+                                           float& acc0, float& acc1) {
+  const uint4 h0 = *reinterpret_cast<const uint4*>(pa), h1 = *reinterpret_cast<const uint4*>(pb);
   // eight 6-bit scales and minima per row, four to a word (get_scale_min_k4 of the reference,
   // quantization.cpp:145-155, applied to four sub-blocks at once)
-  uint32_t scA[2], scB[2], mnA[2], mnB[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const uint32_t y = r.h[i].y, z = r.h[i].z, w = r.h[i].w;
-    scA[i] = y & 0x3F3F3F3Fu;
-    mnA[i] = z & 0x3F3F3F3Fu;
-    scB[i] = (w & 0x0F0F0F0Fu) | ((y >> 2) & 0x30303030u);
-    mnB[i] = ((w >> 4) & 0x0F0F0F0Fu) | ((z >> 2) & 0x30303030u);
-  }
+  const uint32_t scA0 = h0.y & 0x3F3F3F3Fu, mnA0 = h0.z & 0x3F3F3F3Fu;
+  const uint32_t scB0 = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
+  const uint32_t mnB0 = ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u);
+  const uint32_t scA1 = h1.y & 0x3F3F3F3Fu, mnA1 = h1.z & 0x3F3F3F3Fu;
+  const uint32_t scB1 = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
+  const uint32_t mnB1 = ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u);
   int Jlo[4] = {0, 0, 0, 0}, Jhi[4] = {0, 0, 0, 0};
+  const uint8_t* bp = L.bplane + blk * 256;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    const int e = blk * 256 + 64 * c + 8 * L.t;
-    const uint2 bl = b_frag<P>(a, L.g, e), bh = b_frag<P>(a, L.g, e + 32);
+    const uint2 qa = *reinterpret_cast<const uint2*>(pa + 16 + 32 * c + 8 * L.t), qb = *reinterpret_cast<const uint2*>(pb + 16 + 32 * c + 8 * L.t);
+    const uint2 bl = *reinterpret_cast<const uint2*>(bp + 64 * c), bh = *reinterpret_cast<const uint2*>(bp + 64 * c + 32);
     int cl[4], ch[4];
-    imma_16x8x32<false>(cl, r.q[0][c].x & 0x0F0F0F0Fu, r.q[1][c].x & 0x0F0F0F0Fu, r.q[0][c].y & 0x0F0F0F0Fu,
-                        r.q[1][c].y & 0x0F0F0F0Fu, bl.x, bl.y);
-    imma_16x8x32<false>(ch, r.q[0][c].x & 0xF0F0F0F0u, r.q[1][c].x & 0xF0F0F0F0u, r.q[0][c].y & 0xF0F0F0F0u,
-                        r.q[1][c].y & 0xF0F0F0F0u, bh.x, bh.y);  // 16 x the high-nibble sums
-    const int sl0 = byte_u(c < 2 ? scA[0] : scB[0], (2 * c) & 3), sh0 = byte_u(c < 2 ? scA[0] : scB[0], (2 * c + 1) & 3);
-    const int sl1 = byte_u(c < 2 ? scA[1] : scB[1], (2 * c) & 3), sh1 = byte_u(c < 2 ? scA[1] : scB[1], (2 * c + 1) & 3);
+    imma_16x8x32<false>(cl, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu, bl.x, bl.y);
+    imma_16x8x32<false>(ch, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u, bh.x, bh.y);  // 16 x
+    const uint32_t s0 = c < 2 ? scA0 : scB0, s1 = c < 2 ? scA1 : scB1;
+    const int sl0 = byte_u(s0, (2 * c) & 3), sh0 = byte_u(s0, (2 * c + 1) & 3);
+    const int sl1 = byte_u(s1, (2 * c) & 3), sh1 = byte_u(s1, (2 * c + 1) & 3);
     Jlo[0] += sl0 * cl[0]; Jlo[1] += sl0 * cl[1]; Jlo[2] += sl1 * cl[2]; Jlo[3] += sl1 * cl[3];
     Jhi[0] += sh0 * ch[0]; Jhi[1] += sh0 * ch[1]; Jhi[2] += sh1 * ch[2]; Jhi[3] += sh1 * ch[3];
   }
@@ -312,80 +329,53 @@ __device__ __forceinline__ void compute_q4(const RawQ4& r, const ActImage& a, in
   const float f1 = L.wa * fmaf((float)Jhi[2], 0.0625f, (float)Jlo[2]) + L.wb * fmaf((float)Jhi[3], 0.0625f, (float)Jlo[3]);
   // minimum term: sum_sub m_sub * X_sub, digit t of X handled by lane t
   const uint2 xw = *reinterpret_cast<const uint2*>(a.xs32d + (size_t)L.t * a.n32 + blk * 8);
-  const int M0 = dp4a_us(mnB[0], xw.y, dp4a_us(mnA[0], xw.x, 0));
-  const int M1 = dp4a_us(mnB[1], xw.y, dp4a_us(mnA[1], xw.x, 0));
+  const int M0 = dp4a_us(mnB0, xw.y, dp4a_us(mnA0, xw.x, 0));
+  const int M1 = dp4a_us(mnB1, xw.y, dp4a_us(mnA1, xw.x, 0));
   const float sxb = a.sx[blk];
-  const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&r.h[0].x));
-  const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&r.h[1].x));
+  const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
+  const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&h1.x));
   acc0 = fmaf(sxb, dm0.x * f0 - dm0.y * (L.wd * (float)M0), acc0);
   acc1 = fmaf(sxb, dm1.x * f1 - dm1.y * (L.wd * (float)M1), acc1);
-}
-
-struct RawQ6 {
-  uint2 ql[2][4];  // [row][half*2 + (low|high 32 bytes)]
-  uint2 qh[2][2];  // [row][half]
-  uint4 sc[2];
-  uint16_t d[2];
-};
-__device__ __forceinline__ void load_q6(RawQ6& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const RowPtr& rp = i ? rb : ra;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r.ql[i][j] = ldg64_stream(rp.w + (size_t)blk * 128 + 32 * j + 8 * t);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) r.qh[i][h] = ldg64_stream(rp.qh + (size_t)blk * 64 + 32 * h + 8 * t);
-    r.sc[i] = ldg128_stream(rp.sc + (size_t)blk * 16);
-    r.d[i] = ldg16(rp.d + (size_t)blk * 2);
-  }
 }
 
 // Q6_K: a group of 32 consecutive elements holds two 16-element sub-blocks. Lanes t = 0,1 carry
 // the first one, t = 2,3 the second; columns 0..P-1 see only the first (B is zero for t >= 2),
 // columns P..2P-1 only the second, so one instruction yields both sub-block sums separately.
 template <int P>
-__device__ __forceinline__ void compute_q6(const RawQ6& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
+__device__ __forceinline__ void compute_q6(const uint8_t* pa, const uint8_t* pb, float d0, float d1, const ActImage& a, int blk,
+                                           const LaneCtx& L, float& acc0, float& acc1) {
   const int col = L.g, sub_of_col = col / P, plane = col - sub_of_col * P;
   const bool b_on = col < 2 * P && sub_of_col == (L.t >> 1);
-  // which sub-block (0/1) columns 2t and 2t+1 belong to
   const uint32_t selA = (uint32_t)((2 * L.t) / P), selB = (uint32_t)((2 * L.t + 1) / P);
+  const uint8_t* bp = a.planes + (size_t)(b_on ? plane : 0) * a.plane_stride + blk * 256 + 8 * L.t;
+  const uint4 sc0 = *reinterpret_cast<const uint4*>(pa + 192), sc1 = *reinterpret_cast<const uint4*>(pb + 192);
   int J[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    uint32_t hf[2][2][4];  // [row][word][field] : 2-bit fields moved to bits 4-5 of every byte
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const uint32_t hw[2] = {r.qh[i][h].x, r.qh[i][h].y};
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        hf[i][w][0] = (hw[w] << 4) & 0x30303030u;
-        hf[i][w][1] = (hw[w] << 2) & 0x30303030u;
-        hf[i][w][2] = hw[w] & 0x30303030u;
-        hf[i][w][3] = (hw[w] >> 2) & 0x30303030u;
-      }
-    }
+    const uint2 ha = *reinterpret_cast<const uint2*>(pa + 128 + 32 * h + 8 * L.t), hb = *reinterpret_cast<const uint2*>(pb + 128 + 32 * h + 8 * L.t);
+    const uint32_t hw[2][2] = {{ha.x, ha.y}, {hb.x, hb.y}};
 #pragma unroll
     for (int g4 = 0; g4 < 4; ++g4) {
       uint32_t av[2][2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        const uint2 lw = r.ql[i][h * 2 + (g4 & 1)];
+        const uint2 lw = *reinterpret_cast<const uint2*>((i ? pb : pa) + 64 * h + 32 * (g4 & 1) + 8 * L.t);
         const uint32_t l2[2] = {lw.x, lw.y};
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
           const uint32_t nib = g4 < 2 ? (l2[w] & 0x0F0F0F0Fu) : ((l2[w] >> 4) & 0x0F0F0F0Fu);
-          av[i][w] = nib | hf[i][w][g4];
+          const uint32_t hi = g4 == 0 ? (hw[i][w] << 4) : g4 == 1 ? (hw[i][w] << 2) : g4 == 2 ? hw[i][w] : (hw[i][w] >> 2);
+          av[i][w] = nib | (hi & 0x30303030u);
         }
       }
-      const int e = blk * 256 + 128 * h + 32 * g4 + 8 * L.t;
-      uint2 bv = make_uint2(0u, 0u);
-      if (b_on) bv = *reinterpret_cast<const uint2*>(a.planes + (size_t)plane * a.plane_stride + e);
+      uint2 bv = *reinterpret_cast<const uint2*>(bp + 128 * h + 32 * g4);
+      if (!b_on) bv = make_uint2(0u, 0u);
       int c[4];
       imma_16x8x32<false>(c, av[0][0], av[1][0], av[0][1], av[1][1], bv.x, bv.y);
       // sub-scale index within the block: 8h + 2*g4 + (0|1) -> word (2h + g4/2), byte 2(g4&1) + sel
       const int wsel = 2 * h + (g4 >> 1);
-      const uint32_t w0 = wsel == 0 ? r.sc[0].x : wsel == 1 ? r.sc[0].y : wsel == 2 ? r.sc[0].z : r.sc[0].w;
-      const uint32_t w1 = wsel == 0 ? r.sc[1].x : wsel == 1 ? r.sc[1].y : wsel == 2 ? r.sc[1].z : r.sc[1].w;
+      const uint32_t w0 = wsel == 0 ? sc0.x : wsel == 1 ? sc0.y : wsel == 2 ? sc0.z : sc0.w;
+      const uint32_t w1 = wsel == 0 ? sc1.x : wsel == 1 ? sc1.y : wsel == 2 ? sc1.z : sc1.w;
       const uint32_t bA = 2 * (g4 & 1) + selA, bB = 2 * (g4 & 1) + selB;
       J[0] += byte_s(w0, bA) * c[0];
       J[1] += byte_s(w0, bB) * c[1];
@@ -393,40 +383,30 @@ __device__ __forceinline__ void compute_q6(const RawQ6& r, const ActImage& a, in
       J[3] += byte_s(w1, bB) * c[3];
     }
   }
-  const float f0 = L.wa * (float)J[0] + L.wb * (float)J[1];
-  const float f1 = L.wa * (float)J[2] + L.wb * (float)J[3];
+  const float f0 = L.wa6 * (float)J[0] + L.wb6 * (float)J[1];
+  const float f1 = L.wa6 * (float)J[2] + L.wb6 * (float)J[3];
   // offset term: the stored quants are q + 32, so subtract 32 * sum_sub sc_sub * X_sub (digit t per lane)
   const uint4 xw = *reinterpret_cast<const uint4*>(a.xs16d + (size_t)L.t * a.n16 + blk * 16);
-  const int C0 = dp4a_ss(r.sc[0].w, xw.w, dp4a_ss(r.sc[0].z, xw.z, dp4a_ss(r.sc[0].y, xw.y, dp4a_ss(r.sc[0].x, xw.x, 0))));
-  const int C1 = dp4a_ss(r.sc[1].w, xw.w, dp4a_ss(r.sc[1].z, xw.z, dp4a_ss(r.sc[1].y, xw.y, dp4a_ss(r.sc[1].x, xw.x, 0))));
+  const int C0 = dp4a_ss(sc0.w, xw.w, dp4a_ss(sc0.z, xw.z, dp4a_ss(sc0.y, xw.y, dp4a_ss(sc0.x, xw.x, 0))));
+  const int C1 = dp4a_ss(sc1.w, xw.w, dp4a_ss(sc1.z, xw.z, dp4a_ss(sc1.y, xw.y, dp4a_ss(sc1.x, xw.x, 0))));
   const float sxb = a.sx[blk];
-  acc0 = fmaf(sxb * half_bits_to_float(r.d[0]), f0 - 32.f * (L.wd * (float)C0), acc0);
-  acc1 = fmaf(sxb * half_bits_to_float(r.d[1]), f1 - 32.f * (L.wd * (float)C1), acc1);
-}
-
-struct RawQ8 {
-  uint2 q[2][8];
-  uint4 d[2];
-};
-__device__ __forceinline__ void load_q8(RawQ8& r, const RowPtr& ra, const RowPtr& rb, int blk, int t) {
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const RowPtr& rp = i ? rb : ra;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) r.q[i][j] = ldg64_stream(rp.w + (size_t)blk * 256 + 32 * j + 8 * t);
-    r.d[i] = ldg128_stream(rp.d + (size_t)blk * 16);
-  }
+  acc0 = fmaf(sxb * d0, f0 - 32.f * (L.wd * (float)C0), acc0);
+  acc1 = fmaf(sxb * d1, f1 - 32.f * (L.wd * (float)C1), acc1);
 }
 
 template <int P>
-__device__ __forceinline__ void compute_q8(const RawQ8& r, const ActImage& a, int blk, const LaneCtx& L, float& acc0, float& acc1) {
-  const uint32_t dw0[4] = {r.d[0].x, r.d[0].y, r.d[0].z, r.d[0].w}, dw1[4] = {r.d[1].x, r.d[1].y, r.d[1].z, r.d[1].w};
+__device__ __forceinline__ void compute_q8(const uint8_t* pa, const uint8_t* pb, const ActImage& a, int blk, const LaneCtx& L,
+                                           float& acc0, float& acc1) {
+  const uint4 da = *reinterpret_cast<const uint4*>(pa + 256), db = *reinterpret_cast<const uint4*>(pb + 256);
+  const uint32_t dw0[4] = {da.x, da.y, da.z, da.w}, dw1[4] = {db.x, db.y, db.z, db.w};
+  const uint8_t* bp = L.bplane + blk * 256;
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const uint2 bv = b_frag<P>(a, L.g, blk * 256 + 32 * j + 8 * L.t);
+    const uint2 qa = *reinterpret_cast<const uint2*>(pa + 32 * j + 8 * L.t), qb = *reinterpret_cast<const uint2*>(pb + 32 * j + 8 * L.t);
+    const uint2 bv = *reinterpret_cast<const uint2*>(bp + 32 * j);
     int c[4];
-    imma_16x8x32<true>(c, r.q[0][j].x, r.q[1][j].x, r.q[0][j].y, r.q[1][j].y, bv.x, bv.y);
+    imma_16x8x32<true>(c, qa.x, qb.x, qa.y, qb.y, bv.x, bv.y);
     // the scale field of a Q8_0 block is used by magnitude (reference quantization.cpp:85-87)
     const float d0 = scale_field_to_float((uint16_t)((dw0[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
     const float d1 = scale_field_to_float((uint16_t)((dw1[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
@@ -436,37 +416,6 @@ __device__ __forceinline__ void compute_q8(const RawQ8& r, const ActImage& a, in
   const float sxb = a.sx[blk];
   acc0 = fmaf(sxb, s0, acc0);
   acc1 = fmaf(sxb, s1, acc1);
-}
-
-// blocks [blk0, blk1) of one tile for this warp; the next block's loads are in flight while the
-// current one is multiplied (two register buffers used alternately)
-#define B200_SEGMENT_LOOP(RAW, LOAD, COMPUTE)                   \
-  {                                                             \
-    RAW bufA, bufB;                                             \
-    LOAD(bufA, ra, rb, blk0, L.t);                              \
-    int b = blk0;                                               \
-    while (true) {                                              \
-      if (b + 1 < blk1) LOAD(bufB, ra, rb, b + 1, L.t);         \
-      COMPUTE<P>(bufA, a, b, L, acc0, acc1);                    \
-      if (++b >= blk1) break;                                   \
-      if (b + 1 < blk1) LOAD(bufA, ra, rb, b + 1, L.t);         \
-      COMPUTE<P>(bufB, a, b, L, acc0, acc1);                    \
-      if (++b >= blk1) break;                                   \
-    }                                                           \
-  }
-
-template <int P>
-__device__ __forceinline__ void tile_segment(int type, const RowPtr& ra, const RowPtr& rb, const ActImage& a, int blk0, int blk1,
-                                             LaneCtx L, float wa6, float wb6, float& acc0, float& acc1) {
-  if (type == T_Q4_K) {
-    B200_SEGMENT_LOOP(RawQ4, load_q4, compute_q4)
-  } else if (type == T_Q6_K) {
-    L.wa = wa6;
-    L.wb = wb6;
-    B200_SEGMENT_LOOP(RawQ6, load_q6, compute_q6)
-  } else {
-    B200_SEGMENT_LOOP(RawQ8, load_q8, compute_q8)
-  }
 }
 
 // Maps (tile, row-in-tile 0..15) to a segment and a row of it. Ordinary launches: the segments'
@@ -486,83 +435,142 @@ __device__ __forceinline__ void tile_row(const GemvParams& p, int tile, int r, i
   if (!valid) row = p.seg[seg].rows - 1;  // loads stay in bounds; the result is discarded
 }
 
+__host__ __device__ __forceinline__ size_t gemv_ring_offset(int K, int P) { return (act_smem_bytes(K, P) + 127) / 128 * 128; }
+
 template <int P>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm) {
   extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) unsigned long long full_bar[GEMV_MAX_STAGES];
+  __shared__ __align__(8) unsigned long long empty_bar[GEMV_MAX_STAGES];
   __shared__ double red_scratch[34];
-  __shared__ float part[GEMV_WARPS][2][16];
-  __shared__ int part_tile[GEMV_WARPS][2];
+  __shared__ float part[2][GEMV_WARPS][16];
   __shared__ float sv[GEMV_WARPS];
   __shared__ int si[GEMV_WARPS];
+  __shared__ int abort_flag;
   const int bidx = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = prm.nstages, RSS = prm.row_stride;
+  uint8_t* ring = smem + gemv_ring_offset(prm.K, P);
+  const size_t stage_bytes = (size_t)16 * RSS;
+
+  const int nblk = prm.K / 256;
+  const int nslab = (nblk + GEMV_SLAB - 1) / GEMV_SLAB;
+  const int tA = (int)((long long)blockIdx.x * prm.ntiles / gridDim.x);
+  const int tB = (int)((long long)(blockIdx.x + 1) * prm.ntiles / gridDim.x);
+  const int nst_total = (tB - tA) * nslab;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < D; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], GEMV_WARPS);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == GEMV_WARPS) {
+    // ---- producer: lanes 0..15 each copy one row of the tile slab; weights never depend on the
+    // previous kernel, so this starts before the dependency wait of the consumers ----
+    for (int s = 0; s < nst_total; ++s) {
+      const int slot = s % D, use = s / D;
+      if (use > 0) {
+        bool ok = true;
+        if (lane == 0 && !*(volatile int*)&abort_flag) ok = mbar_wait(&empty_bar[slot], (use - 1) & 1);
+        if (!ok) { abort_flag = 1; if (prm.error_flag) atomicExch(prm.error_flag, 1); }
+        __syncwarp();
+      }
+      const int tile = tA + s / nslab, slab = s - (s / nslab) * nslab;
+      const int b0 = slab * GEMV_SLAB, nb = min(GEMV_SLAB, nblk - b0);
+      int seg, row;
+      bool valid;
+      tile_row(prm, tile, lane & 15, seg, row, valid);
+      const int ub = gemv_unit_bytes(prm.seg[seg].type);
+      const uint32_t bytes = (uint32_t)(nb * ub);
+      if (lane == 0) mbar_expect_tx(&full_bar[slot], bytes * 16);
+      __syncwarp();
+      if (lane < 16) {
+        const uint8_t* src = prm.seg[seg].w + ((size_t)row * nblk + b0) * ub;
+        bulk_g2s(ring + slot * stage_bytes + (size_t)lane * RSS, src, bytes, &full_bar[slot]);
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
   act_build<P>(smem, prm.x + (size_t)bidx * prm.x_stride, prm.norm_w, prm.eps, prm.K, red_scratch);
   const ActImage a = act_carve(smem, prm.K, P);
 
   LaneCtx L;
   L.g = lane >> 2;
   L.t = lane & 3;
-  const float pw[4] = {1.f, 256.f, 65536.f, 16777216.f};
   {
+    const float pw[4] = {1.f, 256.f, 65536.f, 16777216.f};
     const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
     L.wa = c0 < P ? pw[c0] : 0.f;
     L.wb = c1 < P ? pw[c1] : 0.f;
+    L.wa6 = c0 < 2 * P ? pw[c0 % P] : 0.f;
+    L.wb6 = c1 < 2 * P ? pw[c1 % P] : 0.f;
     L.wd = pw[L.t];
-  }
-  float wa6, wb6;
-  {
-    const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
-    wa6 = c0 < 2 * P ? pw[c0 % P] : 0.f;
-    wb6 = c1 < 2 * P ? pw[c1 % P] : 0.f;
+    L.bplane = a.planes + (size_t)(L.g < P ? L.g : 0) * a.plane_stride + 8 * L.t;
   }
 
-  const int nblk = prm.K / 256;
-  const int tA = (int)((long long)blockIdx.x * prm.ntiles / gridDim.x);
-  const int tB = (int)((long long)(blockIdx.x + 1) * prm.ntiles / gridDim.x);
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
-
-  for (int tb = tA; tb < tB; tb += GEMV_WARPS) {
-    const int nt = min(GEMV_WARPS, tB - tb);
-    const int total = nt * nblk;
-    const int i0 = (int)((long long)warp * total / GEMV_WARPS), i1 = (int)((long long)(warp + 1) * total / GEMV_WARPS);
-    int nseg_used = 0;
-    for (int i = i0; i < i1;) {
-      const int tl = i / nblk, blk0 = i - tl * nblk;
-      const int blk1 = min(nblk, blk0 + (i1 - i));
-      int segA, rowA, segB, rowB;
-      bool vA, vB;
-      tile_row(prm, tb + tl, L.g, segA, rowA, vA);
-      tile_row(prm, tb + tl, L.g + 8, segB, rowB, vB);
-      const RowPtr ra = row_ptr(prm.seg[segA], rowA, prm.K), rb = row_ptr(prm.seg[segB], rowB, prm.K);
-      float acc0 = 0.f, acc1 = 0.f;
-      tile_segment<P>(prm.seg[segA].type, ra, rb, a, blk0, blk1, L, wa6, wb6, acc0, acc1);
-      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-      if (nseg_used < 2) {
-        if (L.t == 0) {
-          part[warp][nseg_used][L.g] = acc0;
-          part[warp][nseg_used][L.g + 8] = acc1;
-        }
-        if (lane == 0) part_tile[warp][nseg_used] = tl;
-      }
-      ++nseg_used;
-      i += blk1 - blk0;
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int s = 0; s < nst_total; ++s) {
+    const int slot = s % D, use = s / D;
+    const int tl = s / nslab, slab = s - tl * nslab;
+    const int tile = tA + tl;
+    const int b0 = slab * GEMV_SLAB, nb = min(GEMV_SLAB, nblk - b0);
+    int segA, rowA, segB, rowB;
+    bool vA, vB;
+    tile_row(prm, tile, L.g, segA, rowA, vA);
+    tile_row(prm, tile, L.g + 8, segB, rowB, vB);
+    const int type = prm.seg[segA].type;
+    const int blk = b0 + warp;
+    float d0 = 0.f, d1 = 0.f;
+    if (type == T_Q6_K && warp < nb) {  // requested before the wait so its latency hides behind it
+      d0 = half_bits_to_float(ldg16(prm.seg[segA].d + ((size_t)rowA * nblk + blk) * 2));
+      d1 = half_bits_to_float(ldg16(prm.seg[segB].d + ((size_t)rowB * nblk + blk) * 2));
     }
-    if (lane == 0)
-      for (int s = nseg_used; s < 2; ++s) part_tile[warp][s] = -1;
-    __syncthreads();
+    if (!*(volatile int*)&abort_flag) {
+      if (!mbar_wait(&full_bar[slot], use & 1)) {
+        abort_flag = 1;
+        if (prm.error_flag) atomicExch(prm.error_flag, 1);
+      }
+    }
+    if (warp < nb) {
+      const int ub = gemv_unit_bytes(type);
+      const uint8_t* pa = ring + slot * stage_bytes + (size_t)L.g * RSS + (size_t)warp * ub;
+      const uint8_t* pb = pa + (size_t)8 * RSS;
+      if (type == T_Q4_K) compute_q4<P>(pa, pb, a, blk, L, acc0, acc1);
+      else if (type == T_Q6_K) compute_q6<P>(pa, pb, d0, d1, a, blk, L, acc0, acc1);
+      else compute_q8<P>(pa, pb, a, blk, L, acc0, acc1);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+    if (slab != nslab - 1) continue;
 
-    if (warp < nt) {  // warp j finishes tile j of this batch: lanes 0..15 own one row each
+    // ---- tile finished: fold the four k-slices, meet the other warps, finish the rows ----
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    const int pp = tl & 1;
+    if (L.t == 0) {
+      part[pp][warp][L.g] = acc0;
+      part[pp][warp][L.g + 8] = acc1;
+    }
+    acc0 = acc1 = 0.f;
+    consumer_sync();
+    if (warp == (tl & (GEMV_WARPS - 1))) {  // lanes 0..15 own one row each
       const int r = lane & 15;
       float tot = 0.f;
-      for (int w = 0; w < GEMV_WARPS; ++w)
 #pragma unroll
-        for (int s = 0; s < 2; ++s)
-          if (part_tile[w][s] == warp) tot += part[w][s][r];
-      const int tile = tb + warp;
+      for (int w = 0; w < GEMV_WARPS; ++w) tot += part[pp][w][r];
       if (prm.epi == EPI_SWIGLU) {
         // reference model.cpp:734-735 with silu_cpu (utils.cpp:700-707): (g * 1/(1+exp(-g))) * u
         const float u = __shfl_sync(0xffffffffu, tot, (lane & 7) + 8);
@@ -601,7 +609,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
         }
       }
     }
-    __syncthreads();
   }
   if (prm.amax_val) {  // per-CTA (value, first index) of the rows this CTA produced
 #pragma unroll
@@ -611,7 +618,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
       if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
     }
     if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
-    __syncthreads();
+    consumer_sync();
     if (threadIdx.x == 0) {
       float bv = sv[0];
       int bi = si[0];
