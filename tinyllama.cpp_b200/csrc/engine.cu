@@ -27,7 +27,7 @@ static T* dev_alloc(b200_engine* e, size_t n) {
 static void set_gemv_attrs() {
   static bool done = false;
   if (done) return;
-  const int maxb = 208 * 1024;
+  const int maxb = 216 * 1024;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -89,14 +89,13 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
     }
     p.ntiles = (rows + 15) / 16;
   }
-  const int nblk = p.K / 256;
-  p.row_stride = (std::min(nblk, GEMV_SLAB) * max_ub + 127) / 128 * 128 + 32;
-  const size_t ring_off = gemv_ring_offset(p.K, e->P), stage = (size_t)16 * p.row_stride;
-  const size_t budget = 200 * 1024;
-  if (ring_off + 2 * stage > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
-  p.nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / stage);
+  gemv_ring_geometry(p.K, max_ub, p.slab, p.row_stride);
+  const size_t ring_off = gemv_ring_offset(p.K, e->P);
+  const size_t budget = 214 * 1024;
+  if (ring_off + 2 * (size_t)GEMV_SLOT_BYTES > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
+  const int nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / GEMV_SLOT_BYTES);
   p.error_flag = e->d_error;
-  const size_t smem = ring_off + p.nstages * stage;
+  const size_t smem = ring_off + (size_t)nstages * GEMV_SLOT_BYTES;
   const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(gx, batch);
@@ -108,8 +107,8 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = e->use_pdl ? 1 : 0;
-  if (e->P == 2) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2>, p));
-  else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3>, p));
+  if (e->P == 2) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2>, p, nstages));
+  else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3>, p, nstages));
   return gx;
 }
 

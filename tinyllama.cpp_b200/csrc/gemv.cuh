@@ -34,10 +34,12 @@
 namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
-constexpr int GEMV_WARPS = 16;                       // consumer warps; one more warp produces
-constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;
-constexpr int GEMV_SLAB = 16;                        // 256-element blocks per row per stage
-constexpr int GEMV_MAX_STAGES = 4;
+constexpr int GEMV_WARPS = 16;                       // consumer warps
+constexpr int GEMV_PROD_WARPS = 4;                   // producer warps, four tile rows each
+constexpr int GEMV_THREADS = (GEMV_WARPS + GEMV_PROD_WARPS) * 32;
+constexpr int GEMV_SLAB = 16;                        // most 256-element blocks per row per stage (one per consumer warp)
+constexpr int GEMV_MAX_STAGES = 6;
+constexpr int GEMV_SLOT_BYTES = 38 * 1024;           // one ring stage: 16 rows x up to 16 Q4_K blocks (+ row padding)
 
 // Device-resident form of a weight matrix, row-major, one "unit" per 256 elements of a row:
 //   Q4_K  unit = the 144-byte block exactly as in the file
@@ -73,11 +75,20 @@ struct GemvParams {
   int max_pos;
   float* amax_val;      // optional per-CTA argmax partials [batch][gridDim.x]
   int* amax_idx;
+  const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
-  int nstages;          // ring depth
+  int slab;             // 256-element blocks per row per stage (<= GEMV_SLAB)
   int row_stride;       // bytes between rows of a stage in shared memory (= 32 mod 128)
   int* error_flag;      // set when a bounded wait gives up
 };
+
+// Ring geometry of a launch: the widest slab whose 16 padded rows fit one ring slot.
+__host__ __device__ __forceinline__ void gemv_ring_geometry(int K, int max_unit_bytes, int& slab, int& row_stride) {
+  const int nblk = K / 256;
+  slab = nblk < GEMV_SLAB ? nblk : GEMV_SLAB;
+  while (slab > 1 && 16 * ((slab * max_unit_bytes + 127) / 128 * 128 + 32) > GEMV_SLOT_BYTES) --slab;
+  row_stride = (slab * max_unit_bytes + 127) / 128 * 128 + 32;
+}
 
 // ---- shared-memory activation image ------------------------------------------------------
 // planes  [P][plane_stride]   digit bytes, element e of plane p at p*plane_stride + e; the stride
@@ -88,7 +99,7 @@ struct GemvParams {
 __host__ __device__ __forceinline__ int act_plane_stride(int K) { return (K + 127) / 128 * 128 + 32; }
 __host__ __device__ __forceinline__ int act_sx_floats(int K) { return (K / 256 + 3) / 4 * 4; }
 __host__ __device__ __forceinline__ size_t act_smem_bytes(int K, int P) {
-  return (size_t)P * act_plane_stride(K) + (size_t)act_sx_floats(K) * 4 + (size_t)4 * (K / 32) + (size_t)4 * (K / 16);
+  return (size_t)P * act_plane_stride(K) + (size_t)act_sx_floats(K) * 4 + (size_t)4 * (K / 32 + 16) + (size_t)4 * (K / 16 + 16);
 }
 
 struct ActImage {
@@ -108,10 +119,10 @@ __device__ __forceinline__ ActImage act_carve(uint8_t* smem, int K, int P) {
   a.sx = reinterpret_cast<const float*>(p);
   p += act_sx_floats(K) * 4;
   a.xs32d = p;
-  a.n32 = K / 32;
+  a.n32 = K / 32 + 16;  // digit-plane strides are offset by 16 bytes so the four digits fall in different banks
   p += 4 * a.n32;
   a.xs16d = p;
-  a.n16 = K / 16;
+  a.n16 = K / 16 + 16;
   return a;
 }
 
@@ -126,94 +137,129 @@ __device__ __forceinline__ void balanced_digits4(int v, int (&d)[4]) {
   }
 }
 
-// Whole-CTA prologue: optional RMSNorm (reference utils.cpp:648-673: double mean of squares,
-// f = 1/sqrtf((float)mean + eps), out = x*f*w) then quantisation into the image above.
+// Quantises the eight elements v[] this lane holds of 256-element block b (after the optional
+// RMSNorm scaling) and writes the block's digit planes, digit sums and scale.
 template <int P>
-__device__ void act_build(uint8_t* smem, const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
-                          int K, double* red /* 33 doubles of shared scratch */) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = GEMV_WARPS;  // consumer warps only
-  float f = 1.0f;
-  if (norm_w) {
-    float ss = 0.f;
-    for (int i = tid * 4; i < K; i += GEMV_WARPS * 32 * 4) {
-      float4 v = *reinterpret_cast<const float4*>(x + i);
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
-    double ds = (double)ss;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
-    if (lane == 0) red[warp] = ds;
-    consumer_sync();
-    if (warp == 0) {
-      double t = lane < nwarps ? red[lane] : 0.0;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-      if (lane == 0) {
-        float mean = (float)(t / (double)K);
-        reinterpret_cast<float*>(red + 32)[0] = 1.0f / sqrtf(mean + eps);
-      }
-    }
-    consumer_sync();
-    f = reinterpret_cast<float*>(red + 32)[0];
-  }
-  ActImage a = act_carve(smem, K, P);
+__device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int lane, const float (&vin)[8],
+                                                   const float* __restrict__ norm_w, const float4 (&nw)[2], float f) {
   uint8_t* planes = const_cast<uint8_t*>(a.planes);
   float* sx = const_cast<float*>(a.sx);
   uint8_t* xs32d = const_cast<uint8_t*>(a.xs32d);
   uint8_t* xs16d = const_cast<uint8_t*>(a.xs16d);
   // largest magnitude P balanced digits can hold: 127 * (256^P - 1) / 255
   constexpr int QMAX = P == 3 ? 8355711 : (P == 2 ? 32639 : 127);
+  const int e0 = b * 256 + lane * 8;
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = vin[i];
+  if (norm_w) {
+    const float w[8] = {nw[0].x, nw[0].y, nw[0].z, nw[0].w, nw[1].x, nw[1].y, nw[1].z, nw[1].w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * f * w[i];
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = warp_max(amax);
+  const float scale = amax / (float)QMAX;
+  const float inv = amax > 0.f ? (float)QMAX / amax : 0.f;
+  int s8 = 0;
+  uint32_t pw[P][2];
+#pragma unroll
+  for (int p = 0; p < P; ++p) pw[p][0] = pw[p][1] = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int q = __float2int_rn(v[i] * inv);
+    q = max(-QMAX, min(QMAX, q));
+    s8 += q;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int dgt = (int)(int8_t)(q & 0xFF);
+      q = (q - dgt) >> 8;
+      pw[p][i >> 2] |= (uint32_t)(dgt & 0xFF) << (8 * (i & 3));
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < P; ++p)
+    *reinterpret_cast<uint2*>(planes + (size_t)p * a.plane_stride + e0) = make_uint2(pw[p][0], pw[p][1]);
+  const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+  const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+  if ((lane & 1) == 0) {
+    int dg[4];
+    balanced_digits4(s16, dg);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xs16d[i * a.n16 + b * 16 + (lane >> 1)] = (uint8_t)dg[i];
+  }
+  if ((lane & 3) == 0) {
+    int dg[4];
+    balanced_digits4(s32, dg);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xs32d[i * a.n32 + b * 8 + (lane >> 2)] = (uint8_t)dg[i];
+  }
+  if (lane == 0) sx[b] = scale;
+}
+
+// Prologue run by the 16 consumer warps: optional RMSNorm (reference utils.cpp:648-673: mean of
+// squares, f = 1/sqrtf(mean + eps), out = x*f*w) then quantisation into the image above. Each
+// warp owns the 256-element blocks warp, warp+16, ...; the vector is read from global memory once
+// (up to four blocks per warp stay in registers between the two passes).
+// XFN(i) returns element i of the input vector.
+template <int P, typename XFN>
+__device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm_w, float eps, int K, float* red /* 18 floats */) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nblk = K / 256;
-  for (int b = warp; b < nblk; b += nwarps) {
-    const int e0 = b * 256 + lane * 8;
-    float4 v0 = *reinterpret_cast<const float4*>(x + e0), v1 = *reinterpret_cast<const float4*>(x + e0 + 4);
-    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  constexpr int KEEP = 4;
+  float xv[KEEP][8];
+  float4 wv[KEEP][2];  // norm weights, requested together with x so the two latencies overlap
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < KEEP; ++k) {
+    const int b = warp + k * GEMV_WARPS;
+    if (b < nblk && norm_w) {
+      wv[k][0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
+      wv[k][1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KEEP; ++k) {
+    const int b = warp + k * GEMV_WARPS;
+    if (b < nblk) {
+      xfn(b * 256 + lane * 8, xv[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(xv[k][i], xv[k][i], ss);
+    }
+  }
+  for (int b = warp + KEEP * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {  // very long vectors: extra blocks are re-read later
+    float t[8];
+    xfn(b * 256 + lane * 8, t);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(t[i], t[i], ss);
+  }
+  float f = 1.0f;
+  if (norm_w) {
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    consumer_sync();
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) t += (double)red[w];
+    f = 1.0f / sqrtf((float)(t / (double)K) + eps);
+  }
+  const ActImage a = act_carve(smem, K, P);
+#pragma unroll
+  for (int k = 0; k < KEEP; ++k) {
+    const int b = warp + k * GEMV_WARPS;
+    if (b < nblk) act_quantize_block<P>(a, b, lane, xv[k], norm_w, wv[k], f);
+  }
+  for (int b = warp + KEEP * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {
+    float t[8];
+    xfn(b * 256 + lane * 8, t);
+    float4 w2[2];
     if (norm_w) {
-      float4 w0 = *reinterpret_cast<const float4*>(norm_w + e0), w1 = *reinterpret_cast<const float4*>(norm_w + e0 + 4);
-      float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = v[i] * f * w[i];
+      w2[0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
+      w2[1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = warp_max(amax);
-    const float scale = amax / (float)QMAX;
-    const float inv = amax > 0.f ? (float)QMAX / amax : 0.f;
-    int s8 = 0;
-    uint32_t pw[P][2];
-#pragma unroll
-    for (int p = 0; p < P; ++p) pw[p][0] = pw[p][1] = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int q = __float2int_rn(v[i] * inv);
-      q = max(-QMAX, min(QMAX, q));
-      s8 += q;
-#pragma unroll
-      for (int p = 0; p < P; ++p) {
-        const int dgt = (int)(int8_t)(q & 0xFF);
-        q = (q - dgt) >> 8;
-        pw[p][i >> 2] |= (uint32_t)(dgt & 0xFF) << (8 * (i & 3));
-      }
-    }
-#pragma unroll
-    for (int p = 0; p < P; ++p)
-      *reinterpret_cast<uint2*>(planes + (size_t)p * a.plane_stride + e0) = make_uint2(pw[p][0], pw[p][1]);
-    const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
-    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-    if ((lane & 1) == 0) {
-      int dg[4];
-      balanced_digits4(s16, dg);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) xs16d[i * a.n16 + b * 16 + (lane >> 1)] = (uint8_t)dg[i];
-    }
-    if ((lane & 3) == 0) {
-      int dg[4];
-      balanced_digits4(s32, dg);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) xs32d[i * a.n32 + b * 8 + (lane >> 2)] = (uint8_t)dg[i];
-    }
-    if (lane == 0) sx[b] = scale;
+    act_quantize_block<P>(a, b, lane, t, norm_w, w2, f);
   }
   consumer_sync();
 }
@@ -262,14 +308,14 @@ __device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
 // Bounded wait: gives up after a fixed number of probes and reports failure instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
-  for (int i = 0; i < (1 << 20); ++i) {
+  for (int i = 0; i < (1 << 16); ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(20000u)  // park up to ~20 us per probe: waiting warps must not steal issue slots
         : "memory");
     if (ok) return true;
   }
@@ -284,7 +330,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 15, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); }
+// split-phase named barrier over the consumer warps: the warps that only contribute partial sums
+// arrive and move on, the warp that finishes the tile waits for all of them
+constexpr int GEMV_TILE_BARS = 8;  // tiles that may be in flight between the fastest and the slowest warp
+__device__ __forceinline__ void tile_bar_arrive(int id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(GEMV_WARPS * 32) : "memory"); }
+__device__ __forceinline__ void tile_bar_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(GEMV_WARPS * 32) : "memory"); }
 
 // ---- per-format work on one 256-element block of a staged 16-row tile ----------------------
 // Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the tile and the k-slice
@@ -294,7 +345,7 @@ struct LaneCtx {
   int g, t;
   float wa, wb;    // 256^plane of columns 2t, 2t+1 for Q4_K / Q8_0 (0 for unused columns)
   float wa6, wb6;  // the same for the Q6_K column layout
-  float wd;        // 256^t: weight of digit t in the minimum / offset terms
+  float wd;        // 256^t: weight of digit t in the minimum / offset terms (t = lane & 3)
   const uint8_t* bplane;  // digit plane this lane's B column reads (any valid plane for unused columns)
 };
 
@@ -435,199 +486,252 @@ __device__ __forceinline__ void tile_row(const GemvParams& p, int tile, int r, i
   if (!valid) row = p.seg[seg].rows - 1;  // loads stay in bounds; the result is discarded
 }
 
-__host__ __device__ __forceinline__ size_t gemv_ring_offset(int K, int P) { return (act_smem_bytes(K, P) + 127) / 128 * 128; }
 
-template <int P>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) unsigned long long full_bar[GEMV_MAX_STAGES];
-  __shared__ __align__(8) unsigned long long empty_bar[GEMV_MAX_STAGES];
-  __shared__ double red_scratch[34];
-  __shared__ float part[2][GEMV_WARPS][16];
-  __shared__ float sv[GEMV_WARPS];
-  __shared__ int si[GEMV_WARPS];
-  __shared__ int abort_flag;
-  const int bidx = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int D = prm.nstages, RSS = prm.row_stride;
-  uint8_t* ring = smem + gemv_ring_offset(prm.K, P);
-  const size_t stage_bytes = (size_t)16 * RSS;
+// ---- the streaming pipeline ----------------------------------------------------------------
+struct GemvShared {
+  unsigned long long full_bar[GEMV_MAX_STAGES];
+  unsigned long long empty_bar[GEMV_MAX_STAGES];
+  float red[GEMV_WARPS + 2];
+  float part[GEMV_TILE_BARS][GEMV_WARPS][16];
+  float sv[GEMV_WARPS];
+  int si[GEMV_WARPS];
+  int abort_flag;
+};
 
-  const int nblk = prm.K / 256;
-  const int nslab = (nblk + GEMV_SLAB - 1) / GEMV_SLAB;
-  const int tA = (int)((long long)blockIdx.x * prm.ntiles / gridDim.x);
-  const int tB = (int)((long long)(blockIdx.x + 1) * prm.ntiles / gridDim.x);
-  const int nst_total = (tB - tA) * nslab;
+struct PipeCtx {
+  GemvShared* sh;
+  uint8_t* act;   // activation image
+  uint8_t* ring;  // nstages slots of GEMV_SLOT_BYTES
+  int nstages;
+  int slot;       // ring slot of the next stage (producer and consumers count alike)
+  int use;        // how many times the ring has wrapped
+  int gt;         // tiles finished so far
+  __device__ __forceinline__ void next_stage() {
+    if (++slot == nstages) { slot = 0; ++use; }
+  }
+};
 
+__device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
   if (threadIdx.x == 0) {
-    for (int s = 0; s < D; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], GEMV_WARPS);
+    for (int s = 0; s < nstages; ++s) {
+      mbar_init(&sh->full_bar[s], GEMV_PROD_WARPS);
+      mbar_init(&sh->empty_bar[s], GEMV_WARPS);
     }
-    abort_flag = 0;
+    sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_launch_dependents();
+}
 
-  if (warp == GEMV_WARPS) {
-    // ---- producer: lanes 0..15 each copy one row of the tile slab; weights never depend on the
-    // previous kernel, so this starts before the dependency wait of the consumers ----
-    for (int s = 0; s < nst_total; ++s) {
-      const int slot = s % D, use = s / D;
+__device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh) {
+  sh->abort_flag = 1;
+  if (prm.error_flag) atomicExch(prm.error_flag, 1);
+}
+
+// Producer warp pw (0..3): lanes 0..3 copy rows 4*pw .. 4*pw+3 of every stage of this CTA's tiles.
+__device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int pw, int lane, int cta, int ncta) {
+  GemvShared* sh = pc.sh;
+  const int nblk = prm.K / 256, nslab = (nblk + prm.slab - 1) / prm.slab;
+  const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
+  for (int tile = tA; tile < tB; ++tile) {
+    int seg = 0, row = 0;
+    bool valid;
+    tile_row(prm, tile, 4 * pw + (lane & 3), seg, row, valid);
+    const int ub = gemv_unit_bytes(prm.seg[seg].type);
+    const uint8_t* src_row = prm.seg[seg].w + (size_t)row * nblk * ub;
+    for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
+      const int slot = pc.slot, use = pc.use;
       if (use > 0) {
-        bool ok = true;
-        if (lane == 0 && !*(volatile int*)&abort_flag) ok = mbar_wait(&empty_bar[slot], (use - 1) & 1);
-        if (!ok) { abort_flag = 1; if (prm.error_flag) atomicExch(prm.error_flag, 1); }
+        if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
         __syncwarp();
       }
-      const int tile = tA + s / nslab, slab = s - (s / nslab) * nslab;
-      const int b0 = slab * GEMV_SLAB, nb = min(GEMV_SLAB, nblk - b0);
-      int seg, row;
-      bool valid;
-      tile_row(prm, tile, lane & 15, seg, row, valid);
-      const int ub = gemv_unit_bytes(prm.seg[seg].type);
+      const int b0 = slab * prm.slab, nb = min(prm.slab, nblk - b0);
       const uint32_t bytes = (uint32_t)(nb * ub);
-      if (lane == 0) mbar_expect_tx(&full_bar[slot], bytes * 16);
+      if (lane == 0) mbar_expect_tx(&sh->full_bar[slot], bytes * 4);
       __syncwarp();
-      if (lane < 16) {
-        const uint8_t* src = prm.seg[seg].w + ((size_t)row * nblk + b0) * ub;
-        bulk_g2s(ring + slot * stage_bytes + (size_t)lane * RSS, src, bytes, &full_bar[slot]);
-      }
+      if (lane < 4)
+        bulk_g2s(pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)(4 * pw + lane) * prm.row_stride, src_row + (size_t)b0 * ub, bytes,
+                 &sh->full_bar[slot]);
     }
-    return;
   }
+}
 
-  // ---- consumers ----
-  pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
-  act_build<P>(smem, prm.x + (size_t)bidx * prm.x_stride, prm.norm_w, prm.eps, prm.K, red_scratch);
-  const ActImage a = act_carve(smem, prm.K, P);
+// The 16 consumer warps: prologue, then one block column per warp per stage, then the row epilogue.
+template <int P, typename XFN>
+__device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc, XFN xfn, int bidx, int cta, int ncta, float& best_v,
+                                             int& best_i) {
+  GemvShared* sh = pc.sh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red);
+  const ActImage a = act_carve(pc.act, prm.K, P);
 
   LaneCtx L;
   L.g = lane >> 2;
   L.t = lane & 3;
   {
-    const float pw[4] = {1.f, 256.f, 65536.f, 16777216.f};
     const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
-    L.wa = c0 < P ? pw[c0] : 0.f;
-    L.wb = c1 < P ? pw[c1] : 0.f;
-    L.wa6 = c0 < 2 * P ? pw[c0 % P] : 0.f;
-    L.wb6 = c1 < 2 * P ? pw[c1 % P] : 0.f;
-    L.wd = pw[L.t];
+    auto p256 = [](int e) { return __int_as_float((127 + 8 * e) << 23); };  // 256^e
+    L.wa = c0 < P ? p256(c0) : 0.f;
+    L.wb = c1 < P ? p256(c1) : 0.f;
+    L.wa6 = c0 < 2 * P ? p256(c0 % P) : 0.f;
+    L.wb6 = c1 < 2 * P ? p256(c1 % P) : 0.f;
+    L.wd = p256(L.t);
     L.bplane = a.planes + (size_t)(L.g < P ? L.g : 0) * a.plane_stride + 8 * L.t;
   }
+  const int nblk = prm.K / 256, nslab = (nblk + prm.slab - 1) / prm.slab;
+  const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
+  const int RSS = prm.row_stride;
 
-  float best_v = -INFINITY;
-  int best_i = 0x7fffffff;
-  float acc0 = 0.f, acc1 = 0.f;
-  for (int s = 0; s < nst_total; ++s) {
-    const int slot = s % D, use = s / D;
-    const int tl = s / nslab, slab = s - tl * nslab;
-    const int tile = tA + tl;
-    const int b0 = slab * GEMV_SLAB, nb = min(GEMV_SLAB, nblk - b0);
+  for (int tile = tA; tile < tB; ++tile, ++pc.gt) {
     int segA, rowA, segB, rowB;
     bool vA, vB;
     tile_row(prm, tile, L.g, segA, rowA, vA);
     tile_row(prm, tile, L.g + 8, segB, rowB, vB);
     const int type = prm.seg[segA].type;
-    const int blk = b0 + warp;
-    float d0 = 0.f, d1 = 0.f;
-    if (type == T_Q6_K && warp < nb) {  // requested before the wait so its latency hides behind it
-      d0 = half_bits_to_float(ldg16(prm.seg[segA].d + ((size_t)rowA * nblk + blk) * 2));
-      d1 = half_bits_to_float(ldg16(prm.seg[segB].d + ((size_t)rowB * nblk + blk) * 2));
-    }
-    if (!*(volatile int*)&abort_flag) {
-      if (!mbar_wait(&full_bar[slot], use & 1)) {
-        abort_flag = 1;
-        if (prm.error_flag) atomicExch(prm.error_flag, 1);
+    const int ub = gemv_unit_bytes(type);
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
+      const int slot = pc.slot, use = pc.use;
+      const int b0 = slab * prm.slab, nb = min(prm.slab, nblk - b0);
+      const int blk = b0 + warp;
+      float d0 = 0.f, d1 = 0.f;
+      if (type == T_Q6_K && warp < nb) {  // requested before the wait so its latency hides behind it
+        d0 = half_bits_to_float(ldg16(prm.seg[segA].d + ((size_t)rowA * nblk + blk) * 2));
+        d1 = half_bits_to_float(ldg16(prm.seg[segB].d + ((size_t)rowB * nblk + blk) * 2));
       }
+      if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->full_bar[slot], use & 1)) pipe_fail(prm, sh);
+      __syncwarp();  // one lane probes; the rest of the warp parks here
+      if (warp < nb) {
+        const uint8_t* pa = pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)L.g * RSS + (size_t)warp * ub;
+        const uint8_t* pb = pa + (size_t)8 * RSS;
+        if (type == T_Q4_K) compute_q4<P>(pa, pb, a, blk, L, acc0, acc1);
+        else if (type == T_Q6_K) compute_q6<P>(pa, pb, d0, d1, a, blk, L, acc0, acc1);
+        else compute_q8<P>(pa, pb, a, blk, L, acc0, acc1);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->empty_bar[slot]);
     }
-    if (warp < nb) {
-      const int ub = gemv_unit_bytes(type);
-      const uint8_t* pa = ring + slot * stage_bytes + (size_t)L.g * RSS + (size_t)warp * ub;
-      const uint8_t* pb = pa + (size_t)8 * RSS;
-      if (type == T_Q4_K) compute_q4<P>(pa, pb, a, blk, L, acc0, acc1);
-      else if (type == T_Q6_K) compute_q6<P>(pa, pb, d0, d1, a, blk, L, acc0, acc1);
-      else compute_q8<P>(pa, pb, a, blk, L, acc0, acc1);
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[slot]);
-    if (slab != nslab - 1) continue;
-
-    // ---- tile finished: fold the four k-slices, meet the other warps, finish the rows ----
+    // ---- tile finished: fold the four k-slices, hand the partial sums to the finishing warp ----
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    const int pp = tl & 1;
+    // A warp can run at most nstages (< GEMV_TILE_BARS) tiles ahead of the slowest one, so slot and
+    // barrier gt % GEMV_TILE_BARS are free again when they come round.
+    const int pp = pc.gt % GEMV_TILE_BARS;
     if (L.t == 0) {
-      part[pp][warp][L.g] = acc0;
-      part[pp][warp][L.g + 8] = acc1;
+      sh->part[pp][warp][L.g] = acc0;
+      sh->part[pp][warp][L.g + 8] = acc1;
     }
-    acc0 = acc1 = 0.f;
-    consumer_sync();
-    if (warp == (tl & (GEMV_WARPS - 1))) {  // lanes 0..15 own one row each
-      const int r = lane & 15;
-      float tot = 0.f;
+    if (warp != (pc.gt & (GEMV_WARPS - 1))) {
+      __syncwarp();
+      tile_bar_arrive(1 + pp);
+      continue;
+    }
+    tile_bar_sync(1 + pp);  // this warp finishes the tile; lanes 0..15 own one row each
+    const int r = lane & 15;
+    float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < GEMV_WARPS; ++w) tot += part[pp][w][r];
-      if (prm.epi == EPI_SWIGLU) {
-        // reference model.cpp:734-735 with silu_cpu (utils.cpp:700-707): (g * 1/(1+exp(-g))) * u
-        const float u = __shfl_sync(0xffffffffu, tot, (lane & 7) + 8);
-        const int row = tile * 8 + (lane & 7);
-        if (lane < 8 && row < prm.seg[0].rows) {
-          const float sig = 1.0f / (1.0f + expf(-tot));
-          prm.y[(size_t)bidx * prm.y_stride + row] = (tot * sig) * u;
-        }
-      } else {
-        int seg, row;
-        bool valid;
-        tile_row(prm, tile, r, seg, row, valid);
-        const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
-        if (lane < 16 && valid) {
-          if (prm.epi == EPI_RESID) {
-            float* y = prm.y + (size_t)bidx * prm.y_stride + row;
-            *y = *y + tot;
-          } else if (prm.epi == EPI_QKV_ROPE) {
-            float v = tot;
-            if (seg < 2) {  // q and k are rotated in adjacent pairs (reference utils.cpp:428-489)
-              const int pos = prm.positions[bidx];
-              if (pos >= 0 && pos < prm.max_pos) {
-                const int i = (row % prm.head_dim) >> 1;
-                const float2 cs = *reinterpret_cast<const float2*>(prm.rope + ((size_t)pos * (prm.head_dim >> 1) + i) * 2);
-                v = (row & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(tot, cs.x))
-                              : __fsub_rn(__fmul_rn(tot, cs.x), __fmul_rn(other, cs.y));
-              }
+    for (int w = 0; w < GEMV_WARPS; ++w) tot += sh->part[pp][w][r];
+    if (prm.epi == EPI_SWIGLU) {
+      // reference model.cpp:734-735 with silu_cpu (utils.cpp:700-707): (g * 1/(1+exp(-g))) * u
+      const float u = __shfl_sync(0xffffffffu, tot, (lane & 7) + 8);
+      const int row = tile * 8 + (lane & 7);
+      if (lane < 8 && row < prm.seg[0].rows) {
+        const float sig = 1.0f / (1.0f + expf(-tot));
+        prm.y[(size_t)bidx * prm.y_stride + row] = (tot * sig) * u;
+      }
+    } else {
+      int seg, row;
+      bool valid;
+      tile_row(prm, tile, r, seg, row, valid);
+      const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
+      if (lane < 16 && valid) {
+        if (prm.epi == EPI_RESID) {
+          const float* rs = (prm.resid ? prm.resid : prm.y) + (size_t)bidx * prm.y_stride + row;
+          prm.y[(size_t)bidx * prm.y_stride + row] = *rs + tot;
+        } else if (prm.epi == EPI_QKV_ROPE) {
+          float v = tot;
+          if (seg < 2) {  // q and k are rotated in adjacent pairs (reference utils.cpp:428-489)
+            const int pos = prm.positions[bidx];
+            if (pos >= 0 && pos < prm.max_pos) {
+              const int i = (row % prm.head_dim) >> 1;
+              const float2 cs = *reinterpret_cast<const float2*>(prm.rope + ((size_t)pos * (prm.head_dim >> 1) + i) * 2);
+              v = (row & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(tot, cs.x))
+                            : __fsub_rn(__fmul_rn(tot, cs.x), __fmul_rn(other, cs.y));
             }
-            float* dst = seg == 0 ? prm.y + (size_t)bidx * prm.y_stride + row
-                                  : prm.y2 + (size_t)bidx * prm.y2_stride + (seg == 2 ? prm.seg[1].rows : 0) + row;
-            *dst = v;
-          } else {
-            prm.y[(size_t)bidx * prm.y_stride + row] = tot;
-            if (tot > best_v || (tot == best_v && row < best_i)) { best_v = tot; best_i = row; }
           }
+          float* dst = seg == 0 ? prm.y + (size_t)bidx * prm.y_stride + row
+                                : prm.y2 + (size_t)bidx * prm.y2_stride + (seg == 2 ? prm.seg[1].rows : 0) + row;
+          *dst = v;
+        } else {
+          prm.y[(size_t)bidx * prm.y_stride + row] = tot;
+          if (tot > best_v || (tot == best_v && row < best_i)) { best_v = tot; best_i = row; }
         }
       }
     }
   }
-  if (prm.amax_val) {  // per-CTA (value, first index) of the rows this CTA produced
+}
+
+// Per-CTA (value, first index) of the rows this CTA produced, from the per-lane running bests.
+__device__ __forceinline__ void gemv_store_argmax(const GemvParams& prm, GemvShared* sh, float best_v, int best_i, int bidx, int cta,
+                                                  int ncta) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
-    }
-    if (lane == 0) { sv[warp] = best_v; si[warp] = best_i; }
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      float bv = sv[0];
-      int bi = si[0];
-      for (int w = 1; w < GEMV_WARPS; ++w)
-        if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-      prm.amax_val[(size_t)bidx * gridDim.x + blockIdx.x] = bv;
-      prm.amax_idx[(size_t)bidx * gridDim.x + blockIdx.x] = bi;
-    }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
   }
+  if (lane == 0) { sh->sv[warp] = best_v; sh->si[warp] = best_i; }
+  consumer_sync();
+  if (threadIdx.x == 0) {
+    float bv = sh->sv[0];
+    int bi = sh->si[0];
+    for (int w = 1; w < GEMV_WARPS; ++w)
+      if (sh->sv[w] > bv || (sh->sv[w] == bv && sh->si[w] < bi)) { bv = sh->sv[w]; bi = sh->si[w]; }
+    prm.amax_val[(size_t)bidx * ncta + cta] = bv;
+    prm.amax_idx[(size_t)bidx * ncta + cta] = bi;
+  }
+}
+
+__host__ __device__ __forceinline__ size_t gemv_ring_offset(int K, int P) { return (act_smem_bytes(K, P) + 127) / 128 * 128; }
+
+struct XFromGlobal {
+  const float* x;
+  __device__ __forceinline__ void operator()(int e, float (&v)[8]) const {
+    const float4 a = *reinterpret_cast<const float4*>(x + e), b = *reinterpret_cast<const float4*>(x + e + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+
+// One launch = one fused matvec for blockIdx.y's activation vector; one persistent CTA per SM.
+template <int P>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm, int nstages) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ GemvShared sh;
+  PipeCtx pc;
+  pc.sh = &sh;
+  pc.act = smem;
+  pc.ring = smem + gemv_ring_offset(prm.K, P);
+  pc.nstages = nstages;
+  pc.slot = 0;
+  pc.use = 0;
+  pc.gt = 0;
+  pipe_init(&sh, nstages);
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= GEMV_WARPS) {
+    // weights never depend on the previous kernel, so the producers start before the consumers' dependency wait
+    gemv_produce(prm, pc, warp - GEMV_WARPS, lane, blockIdx.x, gridDim.x);
+    return;
+  }
+  pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
+  float best_v = -INFINITY;
+  int best_i = 0x7fffffff;
+  XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
+  gemv_consume<P>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
+  if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
 }
 
 }  // namespace b200
