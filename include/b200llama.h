@@ -120,6 +120,24 @@ int b200_attention_decode(const float* q, const float* k_new, const float* v_new
                           const float* v_cache, int n_ctx, int n_heads, int n_kv_heads, int head_dim,
                           int kv_dtype, int n_splits, float* out);
 
+/* No counterpart in the reference. Decode attention for callers that must not allocate device
+ * memory at the moment of the call (stream capture in progress, memory handed out once by an
+ * external pool, allocator frozen after start-up). All pointers are DEVICE pointers owned by the
+ * caller: q [n_heads][hd]; kv_new = new K rows then new V rows [2][n_kv][hd] (already rotated);
+ * k_cache / v_cache [n_kv][max_ctx][hd] (FP32, or int8 with k_scale / v_scale [n_kv][max_ctx]);
+ * position = one int, the index of the new token (rows 0..position-1 of the caches are read, row
+ * `position` is written); out [n_heads][hd]. The split-K scratch is a fixed array inside the library
+ * (about 1 MiB per GPU, held until the process exits): n_heads * n_splits <= 2048, n_heads <= 512,
+ * head_dim <= 128, anything larger is refused with status 2 and a message. The first call on each
+ * device looks up that array's address and raises the kernel's shared-memory limit; make that call
+ * outside any stream capture. Calls share the scratch, so two calls whose kernels overlap on the GPU
+ * (different streams) race; calls on one stream are safe. The launch is asynchronous on `stream`
+ * (a cudaStream_t, may be NULL). */
+int b200_attention_decode_noalloc(const float* d_q, const float* d_kv_new, void* d_k_cache, void* d_v_cache,
+                                  float* d_k_scale, float* d_v_scale, const int* d_position, int n_heads,
+                                  int n_kv_heads, int head_dim, int max_ctx, int kv_dtype, int n_splits,
+                                  float* d_out, void* stream);
+
 /* Timing and counters for the benchmark harness. */
 int b200_engine_stats(const b200_engine* e, int64_t* kernel_launches_per_step, int64_t* weight_bytes,
                       int64_t* kv_bytes_per_position);

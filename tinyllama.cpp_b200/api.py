@@ -30,7 +30,7 @@ EXPORTS = [
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
     "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_rmsnorm", "b200_attention_decode",
-    "b200_engine_stats", "b200_engine_time_kernel", "b200_nccl_unique_id"]
+    "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_nccl_unique_id"]
 
 _lib = None
 _vp, _i, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
@@ -63,6 +63,7 @@ def lib():
     L.b200_matvec.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _i, _vp]
     L.b200_rmsnorm.argtypes = [_vp, _vp, _i, ctypes.c_float, _vp]
     L.b200_attention_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+    L.b200_attention_decode_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
     L.b200_engine_stats.argtypes = [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.b200_engine_time_kernel.argtypes = [_vp, _i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i64)]
     L.b200_nccl_unique_id.argtypes = [_vp]
@@ -220,3 +221,10 @@ def attention_decode(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv_heads, hea
     _check(lib().b200_attention_decode(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), n_ctx, n_heads,
                                        n_kv_heads, head_dim, kv_dtype, n_splits, _ptr(out)))
     return out
+
+
+def attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v_scale, d_position, n_heads, n_kv_heads,
+                             head_dim, max_ctx, kv_dtype, n_splits, d_out, stream=None):
+    """Allocation-free decode attention on caller-owned DEVICE buffers (integers = device addresses)."""
+    _check(lib().b200_attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v_scale, d_position, n_heads,
+                                               n_kv_heads, head_dim, max_ctx, kv_dtype, n_splits, d_out, stream))

@@ -223,3 +223,4 @@ static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {
 }  // namespace b200
 
 #include "engine_abi.inc"
+#include "engine_noalloc.inc"
