@@ -1,20 +1,22 @@
 // Decode attention over the on-device KV cache with split-K over context length.
 //
-// One CTA = (context split, query head, sequence). Every CTA appends nothing except the one that
-// owns the newest position: the new token's K/V row arrives as FP32 (already rotated) from the QKV
-// kernel, is quantised here when the cache is INT8 (per (position, kv head) absmax scale:
-// scale = absmax/127, or 1 when absmax <= 1e-8; q = clamp(roundf(x/scale), -127, 127) — the
-// arithmetic of the reference quantizer, cuda_kernels.cu:1535-1549 and 1596-1599) and written to
-// the cache by the first query head of the group. Partial (max, sum, output) triples go to a
-// scratch buffer; the last CTA of a head to finish (atomic ticket) merges them in split order,
-// so the result does not depend on scheduling.
+// One work item = (context split, query head, sequence), handled by a group of four warps. The
+// group that owns the newest position also appends it: the new token's K/V row arrives as FP32
+// (already rotated) from the QKV kernel, is quantised here when the cache is INT8 (per (position,
+// kv head) absmax scale: scale = absmax/127, or 1 when absmax <= 1e-8; q = clamp(roundf(x/scale),
+// -127, 127) — the arithmetic of the reference quantizer, cuda_kernels.cu:1535-1549 and 1596-1599)
+// and written to the cache by the first query head of the group. Partial (max, sum, output)
+// triples go to a scratch buffer and are merged in split order, so the result does not depend on
+// scheduling: either by the last group of a head to finish (atomic ticket; stand-alone kernel) or
+// by whoever consumes the attention output next (persistent kernel).
 //
 // Softmax follows the reference CPU code (model.cpp:632-663, utils.cpp:675-698):
 //   s_t = (q . k_t) / sqrt(hd);  p_t = exp(s_t - max);  o = sum p_t v_t / (sum p_t + 1e-9).
 //
 // Cache layout (device-internal): K and V [slot][kv_head][position][head_dim], scales
 // [slot][kv_head][position]. Algorithmic HBM bytes = K and V rows of positions 0..pos-1 of the
-// heads read, plus their scales.
+// heads read, plus their scales. Loads are issued four rows ahead per lane so that a group keeps
+// 16 (INT8) or 4 (FP32) cache rows per warp in flight.
 #pragma once
 #include "common.cuh"
 
@@ -33,23 +35,51 @@ struct AttnParams {
   int nq, nkv, hd, max_ctx, nsplit;
   float* part_o;         // [batch][nq][nsplit][hd]
   float* part_ml;        // [batch][nq][nsplit][2]
-  int* tickets;          // [batch][nq], zero between launches
+  int* tickets;          // [batch][nq], zero between launches (ticket merge only)
   float* out;            // [batch][out_stride]
   int out_stride;
   float att_scale;
 };
 
-__device__ __forceinline__ float i8_at(uint32_t w, int i) { return (float)(int)(int8_t)((w >> (8 * i)) & 0xFF); }
+constexpr int ATTN_GROUP_THREADS = 128;
+constexpr int ATTN_UNROLL = 4;
 
-// KV_I8: int8 rows, 16 elements per lane per load; else FP32 rows, 4 elements per lane.
+__device__ __forceinline__ float i8_at(uint32_t w, int i) { return (float)(int)(int8_t)((w >> (8 * i)) & 0xFF); }
+__device__ __forceinline__ void group_sync(int bar_id) { asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(ATTN_GROUP_THREADS) : "memory"); }
+
+__host__ __device__ __forceinline__ int attn_split_cap(int max_ctx, int nsplit) { return ((max_ctx + nsplit - 1) / nsplit + 31) & ~31; }
+// floats of shared memory one group needs
+__host__ __device__ __forceinline__ size_t attn_group_floats(int hd, int max_ctx, int nsplit) {
+  return (size_t)(3 * hd + 4 * hd + attn_split_cap(max_ctx, nsplit) + 16);
+}
+
+// Merges the per-split partials of (sequence b, head h) in split order.
+__device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, int h, int gtid, int nthr, float* dst) {
+  const size_t pbase = ((size_t)b * prm.nq + h) * prm.nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < prm.nsplit; ++s) M = fmaxf(M, __ldcg(&prm.part_ml[(pbase + s) * 2]));
+  float L = 0.f;
+  for (int s = 0; s < prm.nsplit; ++s) {
+    const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
+    if (ls > 0.f) L += ls * expf(ms - M);
+  }
+  const float inv = 1.0f / (L + 1e-9f);
+  for (int d = gtid; d < prm.hd; d += nthr) {
+    float o = 0.f;
+    for (int s = 0; s < prm.nsplit; ++s) {
+      const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
+      if (ls > 0.f) o = fmaf(expf(ms - M), __ldcg(&prm.part_o[(pbase + s) * prm.hd + d]), o);
+    }
+    dst[d] = o * inv;
+  }
+}
+
+// One (split, head, sequence) item by a group of 128 threads. KV_I8: int8 rows, 16 elements per
+// lane per row; else FP32 rows, 4 elements per lane. sm = this group's shared memory.
 template <bool KV_I8>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) {
-  extern __shared__ __align__(16) float sm[];
-  // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
-  // it still waits for this grid to finish before touching anything produced here
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+__device__ void attn_item(const AttnParams& prm, int split, int h, int b, float* sm, int gtid, int bar_id) {
+  const int lane = gtid & 31, warp = gtid >> 5;
+  constexpr int nwarps = ATTN_GROUP_THREADS / 32;
   const int hd = prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
   const int pos = prm.positions[b], slot = prm.slots[b];
   const int T = pos + 1;
@@ -57,15 +87,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) 
   chunk = (chunk + 31) & ~31;
   const int t0 = split * chunk, t1 = min(T, t0 + chunk);
 
-  float* q_s = sm;               // [hd]
-  float* kn_s = q_s + hd;        // [hd] new K row as the cache will hold it (dequantised when INT8)
-  float* vn_s = kn_s + hd;       // [hd]
-  float* o_s = vn_s + hd;        // [nwarps][hd]
-  float* sc_s = o_s + nwarps * hd;  // [cap]
-  __shared__ float red[8];
-  __shared__ int last_flag;
+  float* q_s = sm;                  // [hd]
+  float* kn_s = q_s + hd;           // [hd] new K row as the cache will hold it (dequantised when INT8)
+  float* vn_s = kn_s + hd;          // [hd]
+  float* o_s = vn_s + hd;           // [nwarps][hd]
+  float* red = o_s + nwarps * hd;   // [16]
+  float* sc_s = red + 16;           // [cap]
 
-  for (int d = tid; d < hd; d += blockDim.x) q_s[d] = prm.q[(size_t)b * prm.q_stride + h * hd + d];
+  for (int d = gtid; d < hd; d += ATTN_GROUP_THREADS) q_s[d] = prm.q[(size_t)b * prm.q_stride + h * hd + d];
 
   const size_t head_row0 = ((size_t)slot * prm.nkv + kvh) * prm.max_ctx;  // row index of position 0
   const bool owns_new = (pos >= t0 && pos < t1);
@@ -95,85 +124,110 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) 
       }
     }
   }
-  __syncthreads();
+  group_sync(bar_id);
 
   constexpr int EPL = KV_I8 ? 16 : 4;   // elements per lane per row
+  constexpr int U = ATTN_UNROLL;
   const int lpp = hd / EPL;             // lanes per position (<= 32)
-  const int ppw = 32 / lpp;             // positions per warp iteration
+  const int ppw = 32 / lpp;             // positions per warp per load
   const int gl = lane % lpp, gi = lane / lpp;
   float qr[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) qr[i] = q_s[gl * EPL + i];
+  const size_t row_bytes = (size_t)hd * (KV_I8 ? 1 : 4);
+  const uint8_t* kbase = reinterpret_cast<const uint8_t*>(prm.k_cache) + head_row0 * row_bytes + gl * 16;
+  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(prm.v_cache) + head_row0 * row_bytes + gl * 16;
 
-  // ---- scores ----
-  for (int tb = t0 + warp * ppw; tb < t1; tb += nwarps * ppw) {
-    const int t = tb + gi;
-    float dot = 0.f;
-    if (t < t1) {
+  // ---- scores: U rows per lane requested before any is used ----
+  for (int tb = t0 + warp * ppw * U; tb < t1; tb += nwarps * ppw * U) {
+    uint4 kw[U];
+    float ks[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * ppw + gi;
+      kw[u] = make_uint4(0u, 0u, 0u, 0u);
+      ks[u] = 1.f;
+      if (t < t1 && t != pos) {
+        kw[u] = ldg128(kbase + (size_t)t * row_bytes);
+        if (KV_I8) ks[u] = __ldg(&prm.k_scale[head_row0 + t]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * ppw + gi;
+      float dot = 0.f;
       if (t == pos) {
 #pragma unroll
         for (int i = 0; i < EPL; ++i) dot = fmaf(qr[i], kn_s[gl * EPL + i], dot);
       } else if (KV_I8) {
-        const uint4 kw = ldg128(reinterpret_cast<const int8_t*>(prm.k_cache) + (head_row0 + t) * hd + gl * 16);
-        const uint32_t w4[4] = {kw.x, kw.y, kw.z, kw.w};
+        const uint32_t w4[4] = {kw[u].x, kw[u].y, kw[u].z, kw[u].w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) dot = fmaf(qr[i], i8_at(w4[i >> 2], i & 3), dot);
+        for (int i = 0; i < 16; ++i) dot = fmaf(qr[i & (EPL - 1)], i8_at(w4[i >> 2], i & 3), dot);
+        dot *= ks[u];
       } else {
-        const float4 kf = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(prm.k_cache) + (head_row0 + t) * hd + gl * 4));
-        dot = fmaf(qr[0], kf.x, fmaf(qr[1], kf.y, fmaf(qr[2], kf.z, qr[3] * kf.w)));
+        dot = fmaf(qr[0], __uint_as_float(kw[u].x), fmaf(qr[1], __uint_as_float(kw[u].y),
+                   fmaf(qr[2], __uint_as_float(kw[u].z), qr[3 & (EPL - 1)] * __uint_as_float(kw[u].w))));
       }
-    }
-    for (int o = lpp >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (t < t1 && gl == 0) {
-      if (KV_I8 && t != pos) dot *= prm.k_scale[head_row0 + t];
-      sc_s[t - t0] = dot * prm.att_scale;
+      for (int o = lpp >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (t < t1 && gl == 0) sc_s[t - t0] = dot * prm.att_scale;
     }
   }
-  __syncthreads();
+  group_sync(bar_id);
 
   // ---- max and exp-sum over this split ----
   const int n = max(t1 - t0, 0);
   float m = -INFINITY;
-  for (int i = tid; i < n; i += blockDim.x) m = fmaxf(m, sc_s[i]);
+  for (int i = gtid; i < n; i += ATTN_GROUP_THREADS) m = fmaxf(m, sc_s[i]);
   m = warp_max(m);
   if (lane == 0) red[warp] = m;
-  __syncthreads();
-  m = red[0];
-  for (int w = 1; w < nwarps; ++w) m = fmaxf(m, red[w]);
-  __syncthreads();
+  group_sync(bar_id);
+  m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   float l = 0.f;
-  for (int i = tid; i < n; i += blockDim.x) {
+  for (int i = gtid; i < n; i += ATTN_GROUP_THREADS) {
     const float p = expf(sc_s[i] - m);
     sc_s[i] = p;
     l += p;
   }
   l = warp_sum(l);
-  if (lane == 0) red[warp] = l;
-  __syncthreads();
-  l = 0.f;
-  for (int w = 0; w < nwarps; ++w) l += red[w];
+  if (lane == 0) red[4 + warp] = l;
+  group_sync(bar_id);
+  l = (red[4] + red[5]) + (red[6] + red[7]);
 
   // ---- weighted sum of V ----
   float acc[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
-  for (int tb = t0 + warp * ppw; tb < t1; tb += nwarps * ppw) {
-    const int t = tb + gi;
-    if (t < t1) {
-      const float p = sc_s[t - t0];
+  for (int tb = t0 + warp * ppw * U; tb < t1; tb += nwarps * ppw * U) {
+    uint4 vw[U];
+    float ps[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * ppw + gi;
+      vw[u] = make_uint4(0u, 0u, 0u, 0u);
+      ps[u] = 0.f;
+      if (t < t1) {
+        ps[u] = sc_s[t - t0];
+        if (t != pos) {
+          vw[u] = ldg128(vbase + (size_t)t * row_bytes);
+          if (KV_I8) ps[u] *= __ldg(&prm.v_scale[head_row0 + t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * ppw + gi;
       if (t == pos) {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) acc[i] = fmaf(p, vn_s[gl * EPL + i], acc[i]);
+        for (int i = 0; i < EPL; ++i) acc[i] = fmaf(ps[u], vn_s[gl * EPL + i], acc[i]);
       } else if (KV_I8) {
-        const uint4 vw = ldg128(reinterpret_cast<const int8_t*>(prm.v_cache) + (head_row0 + t) * hd + gl * 16);
-        const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
-        const float ps = p * prm.v_scale[head_row0 + t];
+        const uint32_t w4[4] = {vw[u].x, vw[u].y, vw[u].z, vw[u].w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = fmaf(ps, i8_at(w4[i >> 2], i & 3), acc[i]);
+        for (int i = 0; i < 16; ++i) acc[i & (EPL - 1)] = fmaf(ps[u], i8_at(w4[i >> 2], i & 3), acc[i & (EPL - 1)]);
       } else {
-        const float4 vf = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(prm.v_cache) + (head_row0 + t) * hd + gl * 4));
-        acc[0] = fmaf(p, vf.x, acc[0]); acc[1] = fmaf(p, vf.y, acc[1]);
-        acc[2] = fmaf(p, vf.z, acc[2]); acc[3] = fmaf(p, vf.w, acc[3]);
+        acc[0] = fmaf(ps[u], __uint_as_float(vw[u].x), acc[0]);
+        acc[1] = fmaf(ps[u], __uint_as_float(vw[u].y), acc[1]);
+        acc[2] = fmaf(ps[u], __uint_as_float(vw[u].z), acc[2]);
+        acc[3 & (EPL - 1)] = fmaf(ps[u], __uint_as_float(vw[u].w), acc[3 & (EPL - 1)]);
       }
     }
   }
@@ -185,50 +239,41 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams prm) 
 #pragma unroll
     for (int i = 0; i < EPL; ++i) o_s[warp * hd + gl * EPL + i] = acc[i];
   }
-  __syncthreads();
+  group_sync(bar_id);
   const size_t pbase = ((size_t)b * prm.nq + h) * prm.nsplit;
-  for (int d = tid; d < hd; d += blockDim.x) {
-    float o = 0.f;
-    for (int w = 0; w < nwarps; ++w) o += o_s[w * hd + d];
-    prm.part_o[(pbase + split) * hd + d] = o;
-  }
-  if (tid == 0) {
+  for (int d = gtid; d < hd; d += ATTN_GROUP_THREADS)
+    prm.part_o[(pbase + split) * hd + d] = (o_s[d] + o_s[hd + d]) + (o_s[2 * hd + d] + o_s[3 * hd + d]);
+  if (gtid == 0) {
     prm.part_ml[(pbase + split) * 2 + 0] = m;
     prm.part_ml[(pbase + split) * 2 + 1] = l;
   }
+}
 
-  // ---- merge: the last CTA of this (sequence, head) combines all splits ----
+// Stand-alone kernel: one group per CTA, ticket merge by the last CTA of each (sequence, head).
+template <bool KV_I8>
+__global__ void __launch_bounds__(ATTN_GROUP_THREADS) attn_decode_kernel(const AttnParams prm) {
+  extern __shared__ __align__(16) float sm[];
+  __shared__ int last_flag;
+  // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
+  // it still waits for this grid to finish before touching anything produced here
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  attn_item<KV_I8>(prm, split, h, b, sm, threadIdx.x, 1);
   __threadfence();
   __syncthreads();
-  if (tid == 0) {
+  if (threadIdx.x == 0) {
     const int old = atomicAdd(&prm.tickets[b * prm.nq + h], 1);
     last_flag = (old == prm.nsplit - 1);
   }
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
-  float M = -INFINITY;
-  for (int s = 0; s < prm.nsplit; ++s) M = fmaxf(M, __ldcg(&prm.part_ml[(pbase + s) * 2]));
-  float L = 0.f;
-  for (int s = 0; s < prm.nsplit; ++s) {
-    const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
-    if (ls > 0.f) L += ls * expf(ms - M);
-  }
-  const float inv = 1.0f / (L + 1e-9f);
-  for (int d = tid; d < hd; d += blockDim.x) {
-    float o = 0.f;
-    for (int s = 0; s < prm.nsplit; ++s) {
-      const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
-      if (ls > 0.f) o = fmaf(expf(ms - M), __ldcg(&prm.part_o[(pbase + s) * hd + d]), o);
-    }
-    prm.out[(size_t)b * prm.out_stride + h * hd + d] = o * inv;
-  }
-  if (tid == 0) prm.tickets[b * prm.nq + h] = 0;
+  attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd);
+  if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
 }
 
-inline size_t attn_smem_bytes(int hd, int max_ctx, int nsplit, int nwarps) {
-  const int cap = ((max_ctx + nsplit - 1) / nsplit + 31) & ~31;
-  return sizeof(float) * (size_t)(3 * hd + nwarps * hd + cap);
+inline size_t attn_smem_bytes(int hd, int max_ctx, int nsplit, int /*nwarps*/) {
+  return sizeof(float) * attn_group_floats(hd, max_ctx, nsplit);
 }
 
 }  // namespace b200

@@ -113,7 +113,7 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 }
 
 static int attn_nsplit(const b200_engine* e, int batch) {
-  int want = (2 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
+  int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
   return std::max(1, std::min(want, 32));
 }
 
