@@ -10,6 +10,7 @@
 #include "dequant.cuh"
 #include "gemv.cuh"
 #include "gguf.h"
+#include "mega.cuh"
 #include "misc.cuh"
 
 namespace b200 {
@@ -30,6 +31,10 @@ static void set_gemv_attrs() {
   const int maxb = 216 * 1024;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((mega_decode_kernel<2, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((mega_decode_kernel<2, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((mega_decode_kernel<3, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((mega_decode_kernel<3, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   done = true;
@@ -89,7 +94,8 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
     }
     p.ntiles = (rows + 15) / 16;
   }
-  gemv_ring_geometry(p.K, max_ub, p.slab, p.row_stride);
+  gemv_ring_geometry(p.K, p);
+  (void)max_ub;
   const size_t ring_off = gemv_ring_offset(p.K, e->P);
   const size_t budget = 214 * 1024;
   if (ring_off + 2 * (size_t)GEMV_SLOT_BYTES > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
@@ -112,9 +118,58 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   return gx;
 }
 
+
 static int attn_nsplit(const b200_engine* e, int batch) {
   int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
   return std::max(1, std::min(want, 32));
+}
+
+// Ring depth the persistent kernel can afford for this model, or 0 when it does not fit.
+static int mega_stage_count(const b200_engine* e) {
+  const size_t ring_off = gemv_ring_offset(std::max(e->F, e->H), e->P);
+  const size_t budget = 214 * 1024;
+  if (ring_off + 2 * (size_t)GEMV_SLOT_BYTES > budget) return 0;
+  if (4 * attn_group_floats(e->hd, e->max_ctx, attn_nsplit(e, 1)) * sizeof(float) > ring_off) return 0;
+  return (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / GEMV_SLOT_BYTES);
+}
+
+// One decode step of a single sequence as ONE cooperative launch (see mega.cuh).
+static int enqueue_mega(b200_engine* e, cudaStream_t st, bool with_embed) {
+  MegaParams mp{};
+  mp.layers = static_cast<const MegaLayer*>(e->d_mega_layers);
+  mp.L = e->L; mp.H = e->H; mp.F = e->F; mp.KVD = e->KVD; mp.nq = e->nq; mp.nkv = e->nkv; mp.hd = e->hd; mp.V = e->V;
+  mp.max_ctx = e->max_ctx; mp.max_pos = e->desc.max_position_embeddings;
+  mp.eps = std::max(e->desc.rms_norm_eps, 1e-5f);
+  mp.att_scale = 1.0f / std::sqrt((float)e->hd);
+  mp.head = seg_of(e->out_w); mp.out_norm = e->out_norm.f32(); mp.embd = e->tok_embd.f32(); mp.rope = e->rope;
+  mp.embed_from_tokens = with_embed ? 1 : 0;
+  mp.tokens = e->d_tokens; mp.positions = e->d_positions; mp.slots = e->d_slots;
+  mp.h = e->d_h; mp.q = e->d_q; mp.kvnew = e->d_kvnew; mp.attn = e->d_attn; mp.act = e->d_act; mp.logits = e->d_logits;
+  mp.part_o = e->d_part_o; mp.part_ml = e->d_part_ml; mp.tickets = e->d_tickets; mp.nsplit = attn_nsplit(e, 1);
+  mp.amax_val = e->d_amax_val; mp.amax_idx = e->d_amax_idx; mp.argmax_out = e->d_argmax; mp.step_counter = e->d_step;
+  mp.forced = e->d_forced; mp.forced_steps = e->d_forced_steps; mp.log = e->d_log; mp.log_cap = e->log_cap;
+  mp.grid_bar = e->d_grid_bar; mp.error_flag = e->d_error; mp.nstages = e->mega_stages;
+  CK(cudaMemsetAsync(e->d_grid_bar, 0, sizeof(unsigned), st));
+  const size_t smem = gemv_ring_offset(std::max(e->F, e->H), e->P) + (size_t)e->mega_stages * GEMV_SLOT_BYTES;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(e->num_sms);
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const bool i8 = e->desc.kv_dtype == B200_KV_I8;
+  if (e->P == 2) {
+    if (i8) CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<2, true>, mp));
+    else CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<2, false>, mp));
+  } else {
+    if (i8) CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<3, true>, mp));
+    else CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<3, false>, mp));
+  }
+  return 1;
 }
 
 // The launch sequence of one decode step for `batch` sequences (also what gets captured).
@@ -125,6 +180,10 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   int launches = 0;
   const int H = e->H, F = e->F, KVD = e->KVD;
   const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
+  if (batch == 1 && e->use_mega && e->mega_stages >= 2) {
+    if (head_ctas_out) *head_ctas_out = e->num_sms;
+    return enqueue_mega(e, st, with_embed);
+  }
   if (with_embed) {
     embed_kernel<<<batch, 256, 0, st>>>(e->d_tokens, e->tok_embd.f32(), e->d_h, H, e->V);
     CK(cudaGetLastError());

@@ -42,6 +42,10 @@ struct b200_engine {
   int H = 0, F = 0, nq = 0, nkv = 0, L = 0, V = 0, hd = 0, KVD = 0, max_ctx = 0, max_seqs = 0, P = 3;
   int num_sms = 148;
   bool use_pdl = true;
+  bool use_mega = true;        // batch-1 steps run as one persistent kernel
+  void* d_mega_layers = nullptr;
+  unsigned* d_grid_bar = nullptr;
+  int mega_stages = 0;
   int* d_error = nullptr;
   bool finalized = false;
   cudaStream_t stream = nullptr;

@@ -39,7 +39,7 @@ constexpr int GEMV_PROD_WARPS = 4;                   // producer warps, four til
 constexpr int GEMV_THREADS = (GEMV_WARPS + GEMV_PROD_WARPS) * 32;
 constexpr int GEMV_SLAB = 16;                        // most 256-element blocks per row per stage (one per consumer warp)
 constexpr int GEMV_MAX_STAGES = 6;
-constexpr int GEMV_SLOT_BYTES = 38 * 1024;           // one ring stage: 16 rows x up to 16 Q4_K blocks (+ row padding)
+constexpr int GEMV_SLOT_BYTES = 54 * 1024;           // one ring stage: 16 rows x up to 16 Q6_K units (+ row padding)
 
 // Device-resident form of a weight matrix, row-major, one "unit" per 256 elements of a row:
 //   Q4_K  unit = the 144-byte block exactly as in the file
@@ -77,17 +77,22 @@ struct GemvParams {
   int* amax_idx;
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
-  int slab;             // 256-element blocks per row per stage (<= GEMV_SLAB)
-  int row_stride;       // bytes between rows of a stage in shared memory (= 32 mod 128)
+  int slab[3];          // 256-element blocks per row per stage (<= GEMV_SLAB), by format (see gemv_type_index)
+  int row_stride[3];    // bytes between rows of a stage in shared memory (= 32 mod 128), by format
   int* error_flag;      // set when a bounded wait gives up
 };
 
-// Ring geometry of a launch: the widest slab whose 16 padded rows fit one ring slot.
-__host__ __device__ __forceinline__ void gemv_ring_geometry(int K, int max_unit_bytes, int& slab, int& row_stride) {
+__host__ __device__ __forceinline__ int gemv_type_index(int type) { return type == T_Q4_K ? 0 : type == T_Q6_K ? 1 : 2; }
+// Ring geometry per weight format: the widest slab whose 16 padded rows fit one ring slot.
+__host__ __device__ __forceinline__ void gemv_ring_geometry(int K, GemvParams& p) {
   const int nblk = K / 256;
-  slab = nblk < GEMV_SLAB ? nblk : GEMV_SLAB;
-  while (slab > 1 && 16 * ((slab * max_unit_bytes + 127) / 128 * 128 + 32) > GEMV_SLOT_BYTES) --slab;
-  row_stride = (slab * max_unit_bytes + 127) / 128 * 128 + 32;
+  const int ubs[3] = {144, 208, 272};
+  for (int i = 0; i < 3; ++i) {
+    int slab = nblk < GEMV_SLAB ? nblk : GEMV_SLAB;
+    while (slab > 1 && 16 * ((slab * ubs[i] + 127) / 128 * 128 + 32) > GEMV_SLOT_BYTES) --slab;
+    p.slab[i] = slab;
+    p.row_stride[i] = (slab * ubs[i] + 127) / 128 * 128 + 32;
+  }
 }
 
 // ---- shared-memory activation image ------------------------------------------------------
@@ -531,13 +536,16 @@ __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh)
 // Producer warp pw (0..3): lanes 0..3 copy rows 4*pw .. 4*pw+3 of every stage of this CTA's tiles.
 __device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int pw, int lane, int cta, int ncta) {
   GemvShared* sh = pc.sh;
-  const int nblk = prm.K / 256, nslab = (nblk + prm.slab - 1) / prm.slab;
+  const int nblk = prm.K / 256;
   const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
   for (int tile = tA; tile < tB; ++tile) {
     int seg = 0, row = 0;
     bool valid;
     tile_row(prm, tile, 4 * pw + (lane & 3), seg, row, valid);
-    const int ub = gemv_unit_bytes(prm.seg[seg].type);
+    const int type = prm.seg[seg].type, ti = gemv_type_index(type);
+    const int ub = gemv_unit_bytes(type);
+    const int slab_blocks = prm.slab[ti], RSS = prm.row_stride[ti];
+    const int nslab = (nblk + slab_blocks - 1) / slab_blocks;
     const uint8_t* src_row = prm.seg[seg].w + (size_t)row * nblk * ub;
     for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
       const int slot = pc.slot, use = pc.use;
@@ -545,12 +553,12 @@ __device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc,
         if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
         __syncwarp();
       }
-      const int b0 = slab * prm.slab, nb = min(prm.slab, nblk - b0);
+      const int b0 = slab * slab_blocks, nb = min(slab_blocks, nblk - b0);
       const uint32_t bytes = (uint32_t)(nb * ub);
       if (lane == 0) mbar_expect_tx(&sh->full_bar[slot], bytes * 4);
       __syncwarp();
       if (lane < 4)
-        bulk_g2s(pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)(4 * pw + lane) * prm.row_stride, src_row + (size_t)b0 * ub, bytes,
+        bulk_g2s(pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)(4 * pw + lane) * RSS, src_row + (size_t)b0 * ub, bytes,
                  &sh->full_bar[slot]);
     }
   }
@@ -578,21 +586,22 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
     L.wd = p256(L.t);
     L.bplane = a.planes + (size_t)(L.g < P ? L.g : 0) * a.plane_stride + 8 * L.t;
   }
-  const int nblk = prm.K / 256, nslab = (nblk + prm.slab - 1) / prm.slab;
+  const int nblk = prm.K / 256;
   const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
-  const int RSS = prm.row_stride;
 
   for (int tile = tA; tile < tB; ++tile, ++pc.gt) {
     int segA, rowA, segB, rowB;
     bool vA, vB;
     tile_row(prm, tile, L.g, segA, rowA, vA);
     tile_row(prm, tile, L.g + 8, segB, rowB, vB);
-    const int type = prm.seg[segA].type;
+    const int type = prm.seg[segA].type, ti = gemv_type_index(type);
     const int ub = gemv_unit_bytes(type);
+    const int slab_blocks = prm.slab[ti], RSS = prm.row_stride[ti];
+    const int nslab = (nblk + slab_blocks - 1) / slab_blocks;
     float acc0 = 0.f, acc1 = 0.f;
     for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
       const int slot = pc.slot, use = pc.use;
-      const int b0 = slab * prm.slab, nb = min(prm.slab, nblk - b0);
+      const int b0 = slab * slab_blocks, nb = min(slab_blocks, nblk - b0);
       const int blk = b0 + warp;
       float d0 = 0.f, d1 = 0.f;
       if (type == T_Q6_K && warp < nb) {  // requested before the wait so its latency hides behind it
