@@ -160,8 +160,17 @@ def main():
         dist.barrier()
     path = model_path(pkg, shape, scheme)
     t_load = time.perf_counter()
+    nccl_id = None
+    if dist:  # tensor parallel over the ranks of this node: rank 0 makes the NCCL id, everyone gets it
+        import torch
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            idt.copy_(torch.tensor(list(pkg.api.nccl_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, src=0)
+        nccl_id = bytes(idt.cpu().tolist())
     eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if kv == "i8" else pkg.KV_F32, max_seqs=batch,
-                               max_ctx=prompt_len + args.steps + warmup + 80, act_planes=args.planes, device=local_rank)
+                               max_ctx=prompt_len + args.steps + warmup + 80, act_planes=args.planes, device=local_rank,
+                               tp_rank=rank, tp_size=world, nccl_id=nccl_id)
     t_load = time.perf_counter() - t_load
     vocab = eng.vocab
     pr = prompts(batch, prompt_len, vocab)
@@ -189,7 +198,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         dist.barrier()
-    tokens_per_s = world * batch * args.steps / (ms / 1000.0)
+    tokens_per_s = batch * args.steps / (ms / 1000.0)  # one tensor-parallel group: the ranks share the same sequences
 
     # ---- end to end through the C ABI with host buffers: token ids in, logits out, host argmax ----
     e2e_steps = min(args.steps, 64)
@@ -201,7 +210,7 @@ def main():
         logits, _ = eng.decode(toks, [pos + i] * batch, want_logits=True, want_argmax=False)
         toks = logits.argmax(axis=1).astype(np.int32)
     e2e_dt = time.perf_counter() - t0
-    e2e_tps = world * batch * e2e_steps / e2e_dt
+    e2e_tps = batch * e2e_steps / e2e_dt
 
     # ---- roofline of the dominant kernel (the fused dequant-GEMV), each kind timed by itself ----
     st = eng.stats()
@@ -218,8 +227,9 @@ def main():
     gemv_launches = sum(v[1] for v in kinds.values())
     achieved = ksum_b / ksum_t / 1e3  # GB/s
     ctx_mid = prompt_len + warmup + args.steps / 2.0
-    step_bytes = st["weight_bytes"] + batch * 4 * eng.hidden + batch * ctx_mid * st["kv_bytes_per_position"]
-    step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9
+    # per-rank shares add up to the whole model over the ranks (norm vectors are replicated: negligible)
+    step_bytes = world * (st["weight_bytes"] + batch * ctx_mid * st["kv_bytes_per_position"]) + batch * 4 * eng.hidden
+    step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9 / world  # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "traffic": None, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
                 "bytes_per_launch": int(ksum_b / gemv_launches), "us_per_launch": round(ksum_t / gemv_launches, 3),
@@ -227,12 +237,12 @@ def main():
                 "step_frac_of_measured_peak": round(step_gbps / peak, 4), "step_frac_of_8TBps": round(step_gbps / 8000.0, 4)}
 
     line = {"metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": f"i{8 * args.planes} activations x packed int weights, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len, "kv_cache": kv,
                        "context_during_timing": [prompt_len + warmup, prompt_len + warmup + args.steps],
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world} (column-split QKV/gate/up/head, row-split O/down, NCCL all-reduce)",
                        "l2": "weights read per step (GBs) exceed the 126 MB L2; no flush needed",
                        "act_planes": args.planes, "load_s": round(t_load, 2), "prefill_s": round(t_prefill, 2)},
             "e2e": {"value": e2e_tps, "unit": "tokens/s", "h2d_bytes_per_step": 12 * batch,

@@ -145,8 +145,16 @@ int b200_engine_stats(const b200_engine* e, int64_t* kernel_launches_per_step, i
  * distinct layers' weights and returns its mean CUDA-event duration and algorithmic bytes. */
 int b200_engine_time_kernel(b200_engine* e, int which, int iters, float* mean_us, int64_t* bytes_per_launch);
 
+/* ---- tensor parallelism inside one node (no counterpart in the reference, whose MPI coordinator,
+ * distributed_coordinator.cpp, only routes whole requests). One engine per GPU/process with
+ * tp_rank/tp_size set and the same nccl_id; every rank uploads the WHOLE tensors (or loads the same
+ * file) and keeps its shard: attn_q/k/v, ffn_gate/up and output by rows, attn_output and ffn_down by
+ * 256-element blocks of the input dimension; two all-reduces per layer plus a gather of the logits.
+ * All ranks must make the same calls with the same arguments. ---- */
 /* Fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and shares the bytes). */
 int b200_nccl_unique_id(uint8_t* out128);
+/* The contiguous share [begin, end) of `units` that rank tp_rank of tp_size owns (used for the FFN blocks). */
+int b200_tp_share(int64_t units, int tp_size, int tp_rank, int64_t* begin, int64_t* end);
 
 #ifdef __cplusplus
 }

@@ -36,7 +36,7 @@ def build_engine(force=False, verbose=False):
         return LIB_ENGINE
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-          ["-o", LIB_ENGINE, os.path.join(CSRC, "engine.cu"), os.path.join(CSRC, "gguf.cpp")]
+          ["-o", LIB_ENGINE, os.path.join(CSRC, "engine.cu"), os.path.join(CSRC, "gguf.cpp"), "-ldl"]
     subprocess.run(cmd, check=True, cwd=CSRC)
     return LIB_ENGINE
 

@@ -30,7 +30,7 @@ EXPORTS = [
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
     "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_rmsnorm", "b200_attention_decode",
-    "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_nccl_unique_id"]
+    "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_nccl_unique_id", "b200_tp_share"]
 
 _lib = None
 _vp, _i, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
@@ -67,6 +67,7 @@ def lib():
     L.b200_engine_stats.argtypes = [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.b200_engine_time_kernel.argtypes = [_vp, _i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i64)]
     L.b200_nccl_unique_id.argtypes = [_vp]
+    L.b200_tp_share.argtypes = [_i64, _i, _i, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     _lib = L
     return L
 
@@ -105,9 +106,12 @@ class Engine:
         self.vocab, self.hidden = d.vocab_size, d.hidden_size
 
     @classmethod
-    def from_gguf(cls, path, kv_dtype=KV_F32, max_seqs=1, max_ctx=0, act_planes=3, device=0):
+    def from_gguf(cls, path, kv_dtype=KV_F32, max_seqs=1, max_ctx=0, act_planes=3, device=0, tp_rank=0, tp_size=1,
+                  nccl_id=None):
         ov = ModelDesc(kv_dtype=kv_dtype, max_seqs=max_seqs, max_ctx=max_ctx, act_planes=act_planes, device=device,
-                       tp_rank=0, tp_size=1)
+                       tp_rank=tp_rank, tp_size=tp_size)
+        if nccl_id is not None:
+            ctypes.memmove(ov.nccl_id, bytes(nccl_id), 128)
         h = _vp()
         _check(lib().b200_engine_load_gguf(os.fsencode(path), ctypes.byref(ov), ctypes.byref(h)))
         return cls(h.value)
@@ -228,3 +232,16 @@ def attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v
     """Allocation-free decode attention on caller-owned DEVICE buffers (integers = device addresses)."""
     _check(lib().b200_attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v_scale, d_position, n_heads,
                                                n_kv_heads, head_dim, max_ctx, kv_dtype, n_splits, d_out, stream))
+
+
+def nccl_unique_id():
+    """128 bytes identifying a new NCCL communicator (rank 0 creates it and shares it with the other ranks)."""
+    buf = (ctypes.c_uint8 * 128)()
+    _check(lib().b200_nccl_unique_id(buf))
+    return bytes(buf)
+
+
+def tp_share(units, tp_size, tp_rank):
+    b, e = _i64(0), _i64(0)
+    _check(lib().b200_tp_share(units, tp_size, tp_rank, ctypes.byref(b), ctypes.byref(e)))
+    return b.value, e.value

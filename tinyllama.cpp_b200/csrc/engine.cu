@@ -12,6 +12,7 @@
 #include "gguf.h"
 #include "mega.cuh"
 #include "misc.cuh"
+#include "tp.h"
 
 namespace b200 {
 
@@ -172,6 +173,16 @@ static int enqueue_mega(b200_engine* e, cudaStream_t st, bool with_embed) {
   return 1;
 }
 
+// Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
+static int tp_reduce_add(b200_engine* e, int batch, cudaStream_t st) {
+  Nccl& n = Nccl::get();
+  const size_t count = (size_t)batch * e->H;
+  n.check(n.AllReduce(e->d_partial, e->d_partial, count, Nccl::kFloat32, Nccl::kSum, e->nccl_comm, st), "ncclAllReduce");
+  add_inplace_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(e->d_h, e->d_partial, (int)count);
+  CK(cudaGetLastError());
+  return 2;
+}
+
 // The launch sequence of one decode step for `batch` sequences (also what gets captured).
 // Per layer: [RMSNorm + QKV + RoPE] -> [KV append + attention] -> [O proj + residual] ->
 // [RMSNorm + gate/up + SwiGLU] -> [down proj + residual]; then [RMSNorm + lm_head + argmax
@@ -180,7 +191,8 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   int launches = 0;
   const int H = e->H, F = e->F, KVD = e->KVD;
   const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
-  if (batch == 1 && e->use_mega && e->mega_stages >= 2) {
+  const bool tp = e->tp_size > 1;
+  if (batch == 1 && e->use_mega && e->mega_stages >= 2 && !tp) {
     if (head_ctas_out) *head_ctas_out = e->num_sms;
     return enqueue_mega(e, st, with_embed);
   }
@@ -195,19 +207,19 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wq); p.seg[1] = seg_of(w.wk); p.seg[2] = seg_of(w.wv); p.nseg = 3;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
-      p.y = e->d_q; p.y_stride = H; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
+      p.y = e->d_q; p.y_stride = e->Hq; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
       p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
       launch_gemv(e, p, batch, st);
       ++launches;
     }
     {
       AttnParams a{};
-      a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = H; a.kvn_stride = 2 * KVD;
+      a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
       a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
       a.positions = e->d_positions; a.slots = e->d_slots;
       a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
       a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
-      a.out = e->d_attn; a.out_stride = H; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
       const size_t smem = attn_smem_bytes(e->hd, e->max_ctx, nsplit, 4);
       dim3 grid(nsplit, e->nq, batch);
       if (e->desc.kv_dtype == B200_KV_I8) attn_decode_kernel<true><<<grid, 128, smem, st>>>(a);
@@ -217,10 +229,11 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     }
     {
       GemvParams p{};
-      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = H; p.x = e->d_attn; p.x_stride = H; p.epi = EPI_RESID;
-      p.y = e->d_h; p.y_stride = H;
+      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->d_attn; p.x_stride = e->Hq; p.epi = tp ? EPI_STORE : EPI_RESID;
+      p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
       launch_gemv(e, p, batch, st);
       ++launches;
+      if (tp) launches += tp_reduce_add(e, batch, st);
     }
     {
       GemvParams p{};
@@ -232,23 +245,34 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     }
     {
       GemvParams p{};
-      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = EPI_RESID;
-      p.y = e->d_h; p.y_stride = H;
+      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = tp ? EPI_STORE : EPI_RESID;
+      p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
       launch_gemv(e, p, batch, st);
       ++launches;
+      if (tp) launches += tp_reduce_add(e, batch, st);
     }
   }
   {
     GemvParams p{};
     p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->d_h; p.x_stride = H;
     p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE;
-    p.y = e->d_logits; p.y_stride = e->V;
-    p.amax_val = e->d_amax_val; p.amax_idx = e->d_amax_idx;
+    // each rank computes its share of the vocabulary; shares and argmax partials are then gathered
+    const size_t half = (size_t)e->max_seqs * e->amax_cap * e->tp_size;
+    p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
+    p.amax_val = tp ? e->d_amax_val + half : e->d_amax_val; p.amax_idx = tp ? e->d_amax_idx + half : e->d_amax_idx;
+    p.amax_row_offset = e->tp_rank * e->Vl;
     const int grid = launch_gemv(e, p, batch, st);
     ++launches;
+    if (tp) {
+      Nccl& n = Nccl::get();
+      n.check(n.AllGather(e->d_logits_local, e->d_logits, (size_t)batch * e->Vl, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
+      n.check(n.AllGather(p.amax_val, e->d_amax_val, (size_t)batch * grid, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
+      n.check(n.AllGather(p.amax_idx, e->d_amax_idx, (size_t)batch * grid, Nccl::kInt32, e->nccl_comm, st), "ncclAllGather");
+      launches += 3;
+    }
     if (head_ctas_out) *head_ctas_out = grid;
     SelectParams s{};
-    s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid; s.batch = batch;
+    s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid * e->tp_size; s.parts_per_rank = grid; s.batch = batch;
     s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
     s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
     select_kernel<<<1, 256, 0, st>>>(s);

@@ -39,7 +39,15 @@ struct StepGraph {
 
 struct b200_engine {
   b200_model_desc desc{};
+  // H and V are the full model widths; Hq, nq, nkv, KVD, F and Vl are this rank's shares under
+  // tensor parallelism (equal to the full values on a single GPU)
   int H = 0, F = 0, nq = 0, nkv = 0, L = 0, V = 0, hd = 0, KVD = 0, max_ctx = 0, max_seqs = 0, P = 3;
+  int Hq = 0, Vl = 0, F_full = 0;
+  int tp_rank = 0, tp_size = 1;
+  int f_blk0 = 0, f_blk1 = 0;  // this rank's range of 256-element blocks of the FFN dimension
+  void* nccl_comm = nullptr;
+  float* d_partial = nullptr;   // [max_seqs][H] partial sums awaiting the all-reduce
+  float* d_logits_local = nullptr;
   int num_sms = 148;
   bool use_pdl = true;
   bool use_mega = true;        // batch-1 steps run as one persistent kernel

@@ -75,6 +75,7 @@ struct GemvParams {
   int max_pos;
   float* amax_val;      // optional per-CTA argmax partials [batch][gridDim.x]
   int* amax_idx;
+  int amax_row_offset;  // added to the row index reported in amax_idx (vocabulary shard offset)
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
   int slab[3];          // 256-element blocks per row per stage (<= GEMV_SLAB), by format (see gemv_type_index)
@@ -675,7 +676,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
           *dst = v;
         } else {
           prm.y[(size_t)bidx * prm.y_stride + row] = tot;
-          if (tot > best_v || (tot == best_v && row < best_i)) { best_v = tot; best_i = row; }
+          const int grow = row + prm.amax_row_offset;
+          if (tot > best_v || (tot == best_v && grow < best_i)) { best_v = tot; best_i = grow; }
         }
       }
     }

@@ -20,9 +20,10 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const float* __rest
 // token while a prompt is being replayed), positions[b] += 1, and the id is appended to the
 // step log. One block; warp w handles sequences w, w+nwarps, ...
 struct SelectParams {
-  const float* amax_val;  // [batch][nparts]
+  const float* amax_val;  // [ranks][batch][parts_per_rank]
   const int* amax_idx;
-  int nparts;
+  int nparts;             // ranks * parts_per_rank
+  int parts_per_rank;
   int batch;
   int* tokens;            // [batch] in: this step's token, out: next step's
   int* positions;         // [batch]
@@ -42,8 +43,9 @@ __global__ void select_kernel(const SelectParams p) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = lane; i < p.nparts; i += 32) {
-      const float v = p.amax_val[(size_t)b * p.nparts + i];
-      const int idx = p.amax_idx[(size_t)b * p.nparts + i];
+      const size_t at = ((size_t)(i / p.parts_per_rank) * p.batch + b) * p.parts_per_rank + (i % p.parts_per_rank);
+      const float v = p.amax_val[at];
+      const int idx = p.amax_idx[at];
       if (v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
     }
 #pragma unroll
@@ -63,6 +65,12 @@ __global__ void select_kernel(const SelectParams p) {
   }
   __syncthreads();
   if (threadIdx.x == 0) *p.step_counter = step + 1;
+}
+
+// h[i] += partial[i]: the residual add after a tensor-parallel all-reduce.
+__global__ void add_inplace_kernel(float* __restrict__ h, const float* __restrict__ partial, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) h[i] = h[i] + partial[i];
 }
 
 // Standalone RMSNorm for the op-level entry point (reference utils.cpp:648-673).
