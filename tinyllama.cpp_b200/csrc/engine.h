@@ -50,7 +50,7 @@ struct b200_engine {
   float* d_logits_local = nullptr;
   int num_sms = 148;
   bool use_pdl = true;
-  bool use_mega = true;        // batch-1 steps run as one persistent kernel
+  bool use_mega = false;       // batch-1 steps as one persistent kernel (B200_MEGA=1); slower than the graph of kernels so far
   void* d_mega_layers = nullptr;
   unsigned* d_grid_bar = nullptr;
   int mega_stages = 0;

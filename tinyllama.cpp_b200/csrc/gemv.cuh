@@ -538,8 +538,9 @@ __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh)
 __device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int pw, int lane, int cta, int ncta) {
   GemvShared* sh = pc.sh;
   const int nblk = prm.K / 256;
-  const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
-  for (int tile = tA; tile < tB; ++tile) {
+  // tiles are dealt round-robin over the CTAs so that launches mixing formats of different cost
+  // (Q6_K tiles take about twice as long as Q4_K ones) stay balanced
+  for (int tile = cta; tile < prm.ntiles; tile += ncta) {
     int seg = 0, row = 0;
     bool valid;
     tile_row(prm, tile, 4 * pw + (lane & 3), seg, row, valid);
@@ -588,9 +589,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
     L.bplane = a.planes + (size_t)(L.g < P ? L.g : 0) * a.plane_stride + 8 * L.t;
   }
   const int nblk = prm.K / 256;
-  const int tA = (int)((unsigned)cta * (unsigned)prm.ntiles / (unsigned)ncta), tB = (int)((unsigned)(cta + 1) * (unsigned)prm.ntiles / (unsigned)ncta);
 
-  for (int tile = tA; tile < tB; ++tile, ++pc.gt) {
+  for (int tile = cta; tile < prm.ntiles; tile += ncta, ++pc.gt) {
     int segA, rowA, segB, rowB;
     bool vA, vB;
     tile_row(prm, tile, L.g, segA, rowA, vA);
