@@ -138,6 +138,22 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
   const uint8_t* kbase = reinterpret_cast<const uint8_t*>(prm.k_cache) + head_row0 * row_bytes + gl * 16;
   const uint8_t* vbase = reinterpret_cast<const uint8_t*>(prm.v_cache) + head_row0 * row_bytes + gl * 16;
 
+  // The V rows of this warp's first batch of positions do not depend on the scores: request them
+  // now so their latency overlaps the whole score / softmax phase.
+  const int tb_first = t0 + warp * ppw * U;
+  uint4 vw0[U];
+  float vs0[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int t = tb_first + u * ppw + gi;
+    vw0[u] = make_uint4(0u, 0u, 0u, 0u);
+    vs0[u] = 1.f;
+    if (t < t1 && t != pos) {
+      vw0[u] = ldg128(vbase + (size_t)t * row_bytes);
+      if (KV_I8) vs0[u] = __ldg(&prm.v_scale[head_row0 + t]);
+    }
+  }
+
   // ---- scores: U rows per lane requested before any is used ----
   for (int tb = t0 + warp * ppw * U; tb < t1; tb += nwarps * ppw * U) {
     uint4 kw[U];
@@ -208,8 +224,13 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
       if (t < t1) {
         ps[u] = sc_s[t - t0];
         if (t != pos) {
-          vw[u] = ldg128(vbase + (size_t)t * row_bytes);
-          if (KV_I8) ps[u] *= __ldg(&prm.v_scale[head_row0 + t]);
+          if (tb == tb_first) {
+            vw[u] = vw0[u];
+            if (KV_I8) ps[u] *= vs0[u];
+          } else {
+            vw[u] = ldg128(vbase + (size_t)t * row_bytes);
+            if (KV_I8) ps[u] *= __ldg(&prm.v_scale[head_row0 + t]);
+          }
         }
       }
     }
@@ -257,6 +278,8 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS) attn_decode_kernel(const A
   // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
   // it still waits for this grid to finish before touching anything produced here
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // when launched as a programmatic dependent itself: q and the new K/V rows belong to the previous kernel until here
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   attn_item<KV_I8>(prm, split, h, b, sm, threadIdx.x, 1);
   __threadfence();

@@ -221,10 +221,18 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
       a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
       const size_t smem = attn_smem_bytes(e->hd, e->max_ctx, nsplit, 4);
-      dim3 grid(nsplit, e->nq, batch);
-      if (e->desc.kv_dtype == B200_KV_I8) attn_decode_kernel<true><<<grid, 128, smem, st>>>(a);
-      else attn_decode_kernel<false><<<grid, 128, smem, st>>>(a);
-      CK(cudaGetLastError());
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(nsplit, e->nq, batch);
+      cfg.blockDim = dim3(ATTN_GROUP_THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = e->use_pdl ? 1 : 0;
+      if (e->desc.kv_dtype == B200_KV_I8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, a));
+      else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a));
       ++launches;
     }
     {
