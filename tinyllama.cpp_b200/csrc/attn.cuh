@@ -282,15 +282,15 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS) attn_decode_kernel(const A
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   attn_item<KV_I8>(prm, split, h, b, sm, threadIdx.x, 1);
-  __threadfence();
-  __syncthreads();
+  __syncthreads();  // every thread's partials are written; one thread publishes them for the whole CTA
   if (threadIdx.x == 0) {
+    __threadfence();
     const int old = atomicAdd(&prm.tickets[b * prm.nq + h], 1);
     last_flag = (old == prm.nsplit - 1);
+    if (last_flag) __threadfence();
   }
   __syncthreads();
   if (!last_flag) return;
-  __threadfence();
   attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd);
   if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
 }

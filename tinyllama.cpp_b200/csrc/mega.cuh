@@ -202,12 +202,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) mega_decode_kernel(const Mega
       for (int item = cta * 4 + grp; item < nitems; item += ncta * 4) {
         const int hq = item / mp.nsplit, split = item - hq * mp.nsplit;
         attn_item<KV_I8>(a, split, hq, 0, gsm, gtid, 9 + grp);
-        __threadfence();
         group_sync(9 + grp);
-        if (gtid == 0) attn_last[grp] = (atomicAdd(&mp.tickets[hq], 1) == mp.nsplit - 1);
+        if (gtid == 0) {
+          __threadfence();
+          attn_last[grp] = (atomicAdd(&mp.tickets[hq], 1) == mp.nsplit - 1);
+          if (attn_last[grp]) __threadfence();
+        }
         group_sync(9 + grp);
         if (attn_last[grp]) {
-          __threadfence();
           attn_merge_head(a, 0, hq, gtid, ATTN_GROUP_THREADS, mp.attn + hq * mp.hd);
           if (gtid == 0) mp.tickets[hq] = 0;
         }
