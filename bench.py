@@ -225,13 +225,22 @@ def main():
         ksum_b += nbytes * per_step
         ksum_t += us * per_step
     gemv_launches = sum(v[1] for v in kinds.values())
+    # DRAM bytes (read + write) per launch from one ncu capture of this workload's four per-layer kinds
+    # (profiles/gemv_kernel_7b_q4km_bs1.txt); the lm_head launch was not captured and is scaled from its
+    # algorithmic bytes by the mean ratio of the others. Other workloads: no capture, null.
+    traffic = None
+    if args.workload == "c3-llama2-7b-q4km-bs1" and world == 1:
+        ncu_mb = {"gate_up_swiglu": 52.047, "qkv_rope": 38.336, "down_proj": 33.959, "o_proj": 10.758}
+        ratio = sum(ncu_mb.values()) * 1e6 / sum(kern[k]["bytes"] for k in ncu_mb)
+        tot = sum(ncu_mb[k] * 1e6 * kinds[k][1] for k in ncu_mb) + ratio * kern["lm_head"]["bytes"]
+        traffic = int(tot / gemv_launches)
     achieved = ksum_b / ksum_t / 1e3  # GB/s
     ctx_mid = prompt_len + warmup + args.steps / 2.0
     # per-rank shares add up to the whole model over the ranks (norm vectors are replicated: negligible)
     step_bytes = world * (st["weight_bytes"] + batch * ctx_mid * st["kv_bytes_per_position"]) + batch * 4 * eng.hidden
     step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9 / world  # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                "traffic": None, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
+                "traffic": traffic, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
                 "bytes_per_launch": int(ksum_b / gemv_launches), "us_per_launch": round(ksum_t / gemv_launches, 3),
                 "kinds": kern, "step_bytes": int(step_bytes), "step_GBps": round(step_gbps, 1),
                 "step_frac_of_measured_peak": round(step_gbps / peak, 4), "step_frac_of_8TBps": round(step_gbps / 8000.0, 4)}

@@ -266,27 +266,3 @@ def test_upload_tensor_path_and_validation(pkg, tiny_models):
     assert np.array_equal(a, b)
     eng.close()
     ref.close()
-
-
-@pytest.mark.parametrize("kv", ["f32", "i8"])
-def test_persistent_kernel_matches_kernel_graph(pkg, tiny_models, monkeypatch, kv):
-    """The opt-in one-kernel-per-token path (B200_MEGA=1) computes exactly what the graph of kernels does."""
-    kvd = pkg.KV_I8 if kv == "i8" else pkg.KV_F32
-    monkeypatch.setenv("B200_MEGA", "1")
-    mega = pkg.Engine.from_gguf(tiny_models[1], kv_dtype=kvd)
-    monkeypatch.setenv("B200_MEGA", "0")
-    graph = pkg.Engine.from_gguf(tiny_models[1], kv_dtype=kvd)
-    prompt = np.arange(20, dtype=np.int32) * 7 % 512
-    a, b = mega.prefill(prompt), graph.prefill(prompt)
-    assert np.array_equal(a, b)
-    tok = int(a.argmax())
-    for pos in range(20, 36):
-        la, ta = mega.decode([tok], [pos])
-        lb, tb = graph.decode([tok], [pos])
-        assert np.array_equal(la, lb) and int(ta[0]) == int(tb[0])
-        tok = int(ta[0])
-    ga, _ = mega.generate_greedy([tok], [36], 8)
-    gb, _ = graph.generate_greedy([tok], [36], 8)
-    assert np.array_equal(ga, gb)
-    mega.close()
-    graph.close()

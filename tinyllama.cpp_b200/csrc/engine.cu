@@ -10,7 +10,6 @@
 #include "dequant.cuh"
 #include "gemv.cuh"
 #include "gguf.h"
-#include "mega.cuh"
 #include "misc.cuh"
 #include "tp.h"
 
@@ -29,80 +28,105 @@ static T* dev_alloc(b200_engine* e, size_t n) {
 static void set_gemv_attrs() {
   static bool done = false;
   if (done) return;
-  const int maxb = 216 * 1024;
-  CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((mega_decode_kernel<2, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((mega_decode_kernel<2, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((mega_decode_kernel<3, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((mega_decode_kernel<3, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  const int maxb = GEMV_SMEM_BUDGET;
+  CK(cudaFuncSetAttribute((gemv_kernel<2, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((gemv_kernel<2, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((gemv_kernel<3, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((gemv_kernel<3, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   done = true;
 }
 
-// Uploads one packed tensor and regroups Q6_K / Q8_0 into aligned 256-element units on the device.
+// Uploads one packed tensor and lays it out on the device as the stage images the matvec kernel
+// streams (Q6_K / Q8_0 are first regrouped into aligned 256-element units). half >= 0: the tensor
+// is the gate (0) or up (1) projection and shares its image with the other one, every 16-row
+// group holding eight gate rows and the same eight up rows.
 static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* host, size_t bytes, int64_t rows, int64_t cols,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int half = -1) {
   const int64_t be = type_block_elems(type), bb = type_block_bytes(type);
   if (cols % 256) throw std::runtime_error("tensor columns must be a multiple of 256");
   const size_t nblk = (size_t)(rows * cols / be);
   if (bytes != nblk * (size_t)bb) throw std::runtime_error("tensor byte count does not match rows x cols for its type");
-  t.type = type; t.rows = rows; t.cols = cols; t.bytes = bytes;
-  t.base = dev_alloc<uint8_t>(e, bytes + 256);
+  const GemvGeom g = gemv_geometry(type, (int)cols);
+  if ((size_t)g.stage_bytes * 2 + gemv_ring_offset((int)cols, 3) > (size_t)GEMV_SMEM_BUDGET)
+    throw std::runtime_error("tensor rows are too long for the matvec kernel's shared memory");
+  if (half >= 0) {
+    if (rows % 8) throw std::runtime_error("gate/up projections need a multiple of 8 rows");
+    if (t.base && (t.type != type || t.rows != rows || t.cols != cols))
+      throw std::runtime_error("ffn_gate and ffn_up must have the same shape and block type");
+    if (t.halves & (1 << half)) throw std::runtime_error("tensor uploaded twice");
+  } else if (t.base) {
+    throw std::runtime_error("tensor uploaded twice");
+  }
+  const int64_t img_rows = half >= 0 ? 2 * rows : rows;
+  const int tile_rows = 16 * g.R;
+  if (!t.base) {
+    t.type = type; t.rows = rows; t.cols = cols; t.bytes = 0; t.img_rows = img_rows;
+    t.tiles = (int)((img_rows + tile_rows - 1) / tile_rows);
+    const size_t img_bytes = (size_t)t.tiles * g.tile_bytes;
+    t.base = dev_alloc<uint8_t>(e, img_bytes + 256);
+    CK(cudaMemsetAsync(t.base, 0, img_bytes + 256, stream));
+  }
+  t.bytes += bytes;
+  if (half >= 0) t.halves |= 1 << half;
+  uint8_t* raw = nullptr;
+  uint8_t* units = nullptr;
+  uint16_t* dsrc = nullptr;
+  CK(cudaMalloc((void**)&raw, bytes + 16));
+  CK(cudaMemcpyAsync(raw, host, bytes, cudaMemcpyHostToDevice, stream));
+  const size_t n256 = (size_t)(rows * cols / 256);
+  const uint8_t* usrc = raw;
   if (type == T_Q6_K || type == T_Q8_0) {
-    uint8_t* stage = nullptr;
-    CK(cudaMalloc((void**)&stage, bytes));
-    CK(cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, stream));
+    CK(cudaMalloc((void**)&units, n256 * g.ub + 16));
     const unsigned grid = (unsigned)((bytes + 255) / 256);
     if (type == T_Q6_K) {
-      t.d = t.base + (nblk * 208 + 15) / 16 * 16;
-      split_q6_k_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base, t.d);
+      CK(cudaMalloc((void**)&dsrc, n256 * 2 + 16));
+      split_q6_k_kernel<<<grid, 256, 0, stream>>>(raw, nblk, units, reinterpret_cast<uint8_t*>(dsrc));
     } else {
-      regroup_q8_0_kernel<<<grid, 256, 0, stream>>>(stage, nblk, t.base);
+      regroup_q8_0_kernel<<<grid, 256, 0, stream>>>(raw, nblk, units);
     }
     CK(cudaGetLastError());
-    CK(cudaStreamSynchronize(stream));
-    CK(cudaFree(stage));
-  } else {
-    CK(cudaMemcpyAsync(t.base, host, bytes, cudaMemcpyHostToDevice, stream));
-    CK(cudaStreamSynchronize(stream));
+    usrc = units;
   }
+  stage_image_kernel<<<1184, 256, 0, stream>>>(usrc, dsrc, rows, g, half, t.base);
+  CK(cudaGetLastError());
+  CK(cudaStreamSynchronize(stream));
+  CK(cudaFree(raw));
+  if (units) CK(cudaFree(units));
+  if (dsrc) CK(cudaFree(dsrc));
 }
 
 static GemvSeg seg_of(const DevTensor& t) {
+  const GemvGeom g = gemv_geometry(t.type, (int)t.cols);
   GemvSeg s;
-  s.w = t.base; s.d = t.d; s.type = t.type; s.rows = (int)t.rows;
+  s.img = t.base; s.type = t.type; s.rows = (int)t.img_rows; s.tiles = t.tiles;
+  s.RS = g.RS; s.RS_last = g.RS_last; s.d_off = g.d_off; s.d_off_last = g.d_off_last;
+  s.stage_bytes = g.stage_bytes; s.stage_bytes_last = g.stage_bytes_last; s.tile_bytes = g.tile_bytes;
   return s;
 }
 
-// Fills in the tile count and ring geometry, checks the launch's shape rules and starts the
-// kernel with one persistent CTA per SM (fewer when there are fewer tiles), as a programmatic
-// dependent launch when the engine allows it. Returns the grid width.
+// Fills in the launch geometry (tiles, ring slot size and depth), and starts the kernel with one
+// persistent CTA per SM (fewer when there are fewer tiles), as a programmatic dependent launch
+// when the engine allows it. Returns the grid width.
 static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream_t st) {
   if (p.K % 256) throw std::runtime_error("gemv: K must be a multiple of 256");
-  int max_ub = 0;
-  for (int s = 0; s < p.nseg; ++s) max_ub = std::max(max_ub, gemv_unit_bytes(p.seg[s].type));
-  if (p.epi == EPI_SWIGLU) {
-    if (p.nseg != 2 || p.seg[0].rows != p.seg[1].rows || p.seg[0].type != p.seg[1].type)
-      throw std::runtime_error("gemv: gate and up must have the same shape and block type");
-    p.ntiles = (p.seg[0].rows + 7) / 8;
-  } else {
-    int rows = 0;
-    for (int s = 0; s < p.nseg; ++s) {
-      if (s + 1 < p.nseg && p.seg[s].rows % 16) throw std::runtime_error("gemv: segment rows must be a multiple of 16");
-      rows += p.seg[s].rows;
-    }
-    p.ntiles = (rows + 15) / 16;
+  const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
+  p.nblk = g0.nblk; p.nslab = g0.nslab; p.S = g0.S; p.S_last = g0.S_last; p.R = g0.R;
+  p.ntiles = 0;
+  uint32_t slot = 0;
+  for (int s = 0; s < p.nseg; ++s) {
+    p.ntiles += p.seg[s].tiles;
+    slot = std::max(slot, std::max(p.seg[s].stage_bytes, p.seg[s].stage_bytes_last));
   }
-  gemv_ring_geometry(p.K, p);
-  (void)max_ub;
+  if (p.epi == EPI_SWIGLU && p.nseg != 1) throw std::runtime_error("gemv: SwiGLU takes the combined gate+up image");
+  p.slot_bytes = (slot + 127) / 128 * 128;
   const size_t ring_off = gemv_ring_offset(p.K, e->P);
-  const size_t budget = 214 * 1024;
-  if (ring_off + 2 * (size_t)GEMV_SLOT_BYTES > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
-  const int nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / GEMV_SLOT_BYTES);
+  const size_t budget = GEMV_SMEM_BUDGET;
+  if (ring_off + 2 * (size_t)p.slot_bytes > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
+  const int nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / p.slot_bytes);
   p.error_flag = e->d_error;
-  const size_t smem = ring_off + (size_t)nstages * GEMV_SLOT_BYTES;
+  const size_t smem = ring_off + (size_t)nstages * p.slot_bytes;
   const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(gx, batch);
@@ -114,8 +138,14 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = e->use_pdl ? 1 : 0;
-  if (e->P == 2) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2>, p, nstages));
-  else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3>, p, nstages));
+  const bool breg = p.nslab == 1;
+  if (e->P == 2) {
+    if (breg) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2, true>, p, nstages));
+    else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2, false>, p, nstages));
+  } else {
+    if (breg) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3, true>, p, nstages));
+    else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3, false>, p, nstages));
+  }
   return gx;
 }
 
@@ -123,54 +153,6 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 static int attn_nsplit(const b200_engine* e, int batch) {
   int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
   return std::max(1, std::min(want, 32));
-}
-
-// Ring depth the persistent kernel can afford for this model, or 0 when it does not fit.
-static int mega_stage_count(const b200_engine* e) {
-  const size_t ring_off = gemv_ring_offset(std::max(e->F, e->H), e->P);
-  const size_t budget = 214 * 1024;
-  if (ring_off + 2 * (size_t)GEMV_SLOT_BYTES > budget) return 0;
-  if (4 * attn_group_floats(e->hd, e->max_ctx, attn_nsplit(e, 1)) * sizeof(float) > ring_off) return 0;
-  return (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / GEMV_SLOT_BYTES);
-}
-
-// One decode step of a single sequence as ONE cooperative launch (see mega.cuh).
-static int enqueue_mega(b200_engine* e, cudaStream_t st, bool with_embed) {
-  MegaParams mp{};
-  mp.layers = static_cast<const MegaLayer*>(e->d_mega_layers);
-  mp.L = e->L; mp.H = e->H; mp.F = e->F; mp.KVD = e->KVD; mp.nq = e->nq; mp.nkv = e->nkv; mp.hd = e->hd; mp.V = e->V;
-  mp.max_ctx = e->max_ctx; mp.max_pos = e->desc.max_position_embeddings;
-  mp.eps = std::max(e->desc.rms_norm_eps, 1e-5f);
-  mp.att_scale = 1.0f / std::sqrt((float)e->hd);
-  mp.head = seg_of(e->out_w); mp.out_norm = e->out_norm.f32(); mp.embd = e->tok_embd.f32(); mp.rope = e->rope;
-  mp.embed_from_tokens = with_embed ? 1 : 0;
-  mp.tokens = e->d_tokens; mp.positions = e->d_positions; mp.slots = e->d_slots;
-  mp.h = e->d_h; mp.q = e->d_q; mp.kvnew = e->d_kvnew; mp.attn = e->d_attn; mp.act = e->d_act; mp.logits = e->d_logits;
-  mp.part_o = e->d_part_o; mp.part_ml = e->d_part_ml; mp.tickets = e->d_tickets; mp.nsplit = attn_nsplit(e, 1);
-  mp.amax_val = e->d_amax_val; mp.amax_idx = e->d_amax_idx; mp.argmax_out = e->d_argmax; mp.step_counter = e->d_step;
-  mp.forced = e->d_forced; mp.forced_steps = e->d_forced_steps; mp.log = e->d_log; mp.log_cap = e->log_cap;
-  mp.grid_bar = e->d_grid_bar; mp.error_flag = e->d_error; mp.nstages = e->mega_stages;
-  CK(cudaMemsetAsync(e->d_grid_bar, 0, sizeof(unsigned), st));
-  const size_t smem = gemv_ring_offset(std::max(e->F, e->H), e->P) + (size_t)e->mega_stages * GEMV_SLOT_BYTES;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(e->num_sms);
-  cfg.blockDim = dim3(GEMV_THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const bool i8 = e->desc.kv_dtype == B200_KV_I8;
-  if (e->P == 2) {
-    if (i8) CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<2, true>, mp));
-    else CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<2, false>, mp));
-  } else {
-    if (i8) CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<3, true>, mp));
-    else CK(cudaLaunchKernelEx(&cfg, mega_decode_kernel<3, false>, mp));
-  }
-  return 1;
 }
 
 // Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
@@ -192,10 +174,6 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   const int H = e->H, F = e->F, KVD = e->KVD;
   const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
   const bool tp = e->tp_size > 1;
-  if (batch == 1 && e->use_mega && e->mega_stages >= 2 && !tp) {
-    if (head_ctas_out) *head_ctas_out = e->num_sms;
-    return enqueue_mega(e, st, with_embed);
-  }
   if (with_embed) {
     embed_kernel<<<batch, 256, 0, st>>>(e->d_tokens, e->tok_embd.f32(), e->d_h, H, e->V);
     CK(cudaGetLastError());
@@ -245,7 +223,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     }
     {
       GemvParams p{};
-      p.seg[0] = seg_of(w.wgate); p.seg[1] = seg_of(w.wup); p.nseg = 2;
+      p.seg[0] = seg_of(w.wgu); p.nseg = 1;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
       p.y = e->d_act; p.y_stride = F;
       launch_gemv(e, p, batch, st);

@@ -12,16 +12,18 @@ namespace b200 {
 
 struct DevTensor {
   int type = -1;
-  int64_t rows = 0, cols = 0;
-  uint8_t* base = nullptr;  // 256-element units (see gemv_unit_bytes) or F32 data
-  uint8_t* d = nullptr;     // Q6_K: fp16 block scales [rows][K/256]
-  size_t bytes = 0;
+  int64_t rows = 0, cols = 0;  // logical shape
+  uint8_t* base = nullptr;     // packed types: stage images (see gemv.cuh); F32: the data
+  size_t bytes = 0;            // packed bytes as in the file (the algorithmic byte count)
+  int64_t img_rows = 0;        // rows the image holds data for (2 x rows for the gate+up image)
+  int tiles = 0;               // image tiles of 16*R rows
+  int halves = 0;              // gate+up image: which halves have arrived (bit 0 gate, bit 1 up)
   bool present() const { return base != nullptr; }
   const float* f32() const { return reinterpret_cast<const float*>(base); }
 };
 
 struct LayerW {
-  DevTensor attn_norm, wq, wk, wv, wo, ffn_norm, wgate, wup, wdown;
+  DevTensor attn_norm, wq, wk, wv, wo, ffn_norm, wgu /* gate and up, interleaved by 8 rows */, wdown;
   void* k_cache = nullptr;
   void* v_cache = nullptr;
   float* k_scale = nullptr;
@@ -50,10 +52,6 @@ struct b200_engine {
   float* d_logits_local = nullptr;
   int num_sms = 148;
   bool use_pdl = true;
-  bool use_mega = false;       // batch-1 steps as one persistent kernel (B200_MEGA=1); slower than the graph of kernels so far
-  void* d_mega_layers = nullptr;
-  unsigned* d_grid_bar = nullptr;
-  int mega_stages = 0;
   int* d_error = nullptr;
   bool finalized = false;
   cudaStream_t stream = nullptr;

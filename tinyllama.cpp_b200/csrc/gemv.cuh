@@ -4,29 +4,31 @@
 // Arithmetic. The activation vector is quantised once per CTA into P balanced base-256 digit
 // planes (x ~ sx[blk] * x_int, x_int = sum_p digit_p * 256^p, every digit a signed byte, one scale
 // per 256 elements; P = 3 gives 24-bit activations, i.e. FP32-grade). Weights stay the integers
-// that are stored in the blocks. A warp owns a tile of 16 output rows and walks along K one
-// 256-element block at a time; every 32 elements it issues one integer tensor-core instruction
-// (mma.sync m16n8k32, u8/s8 x s8 -> s32) whose 16 x 32 A operand is built in registers from the
-// packed nibbles / 6-bit fields with a couple of logic ops, and whose B operand is the digit
-// planes (one column per plane) read from shared memory. The exact integer sub-block sums are
-// multiplied by the integer sub-block scales (6-bit for Q4_K, int8 for Q6_K) with integer
-// multiply-adds; one float multiply per (row, 256-block) applies the fp16 block scale. The
-// Q4_K minimum term and the Q6_K "-32" offset use per-sub-block sums of the activations, also
-// kept as digit bytes, and are evaluated with dp4a. Rows are finished with warp shuffles.
+// that are stored in the blocks. A warp owns one 256-element block column of a 16-row group;
+// every 32 elements it issues one integer tensor-core instruction (mma.sync m16n8k32, u8/s8 x s8
+// -> s32) whose 16 x 32 A operand is built in registers from the packed nibbles / 6-bit fields
+// with a few logic ops, and whose B columns are the digit planes. The exact integer sub-block
+// sums are multiplied by the integer sub-block scales (6-bit for Q4_K, int8 for Q6_K) with
+// integer multiply-adds; one float multiply per (row, 256-block) applies the fp16 block scale.
+// The Q4_K minimum term and the Q6_K "-32" offset use per-sub-block sums of the activations, also
+// kept as digit bytes, and are evaluated with dp4a.
 //
-// Data movement. One persistent CTA per SM takes a contiguous range of 16-row tiles. A producer
-// warp streams every tile into a ring of shared-memory stages with bulk asynchronous copies
-// (cp.async.bulk, completion on an mbarrier): one copy per row of up to 16 consecutive blocks, so
-// HBM sees long contiguous runs (a whole 16-row tile of a 4096-wide Q4_K matrix is 36 KB of
-// consecutive addresses) and several stages are in flight without holding registers. The 16
-// consumer warps each take one 256-element block column of the staged tile, build their mma
-// operands from shared memory, and their partial row sums meet in a fixed order (deterministic).
-// The first stages are requested before the activation prologue runs, and the kernel supports
-// programmatic dependent launch: weights are prefetched while the previous kernel drains, and
-// only then does it wait for that kernel's results.
+// Data movement. Weights live in HBM as "stage images": the matrix is cut into tiles of 16*R
+// rows and slabs of S <= 16 blocks along K, and each (tile, slab) is stored as one contiguous
+// run laid out exactly as it will sit in shared memory (rows padded to a stride = 32 mod 128 so
+// the fragment loads are free of bank conflicts). One persistent CTA per SM walks its tiles; a
+// single producer thread moves every stage with ONE bulk asynchronous copy (cp.async.bulk,
+// completion counted on an mbarrier) into a ring of shared-memory slots, so HBM sees runs of
+// 20-70 KB and several stages are in flight without holding registers. The 16 consumer warps
+// each take one (row group, block) task of the staged slab. When a row has at most 16 blocks a
+// warp meets the same block column in every tile, and its B fragments (the activation digits)
+// stay in registers for the whole launch. Partial row sums are parked in shared memory and the
+// rows of up to 16 tiles are finished together, in a fixed order (deterministic), by all threads.
+// The kernel supports programmatic dependent launch: weights are prefetched while the previous
+// kernel drains, and only then does it wait for that kernel's results.
 //
-// HBM traffic per launch = the packed bytes of the rows (each read exactly once) plus the
-// activation vector; that is the algorithmic byte count.
+// HBM traffic per launch = the packed bytes of the rows (each read exactly once, plus the row
+// padding: 1.4 % for a 4096-wide Q4_K matrix) plus the activation vector.
 #pragma once
 #include "common.cuh"
 #include "dequant.cuh"
@@ -34,32 +36,113 @@
 namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
-constexpr int GEMV_WARPS = 16;                       // consumer warps
-constexpr int GEMV_PROD_WARPS = 4;                   // producer warps, four tile rows each
-constexpr int GEMV_THREADS = (GEMV_WARPS + GEMV_PROD_WARPS) * 32;
-constexpr int GEMV_SLAB = 16;                        // most 256-element blocks per row per stage (one per consumer warp)
-constexpr int GEMV_MAX_STAGES = 6;
-constexpr int GEMV_SLOT_BYTES = 54 * 1024;           // one ring stage: 16 rows x up to 16 Q6_K units (+ row padding)
+constexpr int GEMV_WARPS = 16;                        // consumer warps
+constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;   // + one producer warp
+constexpr int GEMV_MAX_STAGES = 8;
+constexpr int GEMV_NTB = 16;                          // tiles whose partial sums are parked before their rows are finished
+constexpr int GEMV_SMEM_BUDGET = 208 * 1024;          // dynamic shared memory (activation image + ring)
 
-// Device-resident form of a weight matrix, row-major, one "unit" per 256 elements of a row:
+// One "unit" per 256 elements of a row:
 //   Q4_K  unit = the 144-byte block exactly as in the file
-//   Q6_K  unit = 208 bytes: ql[128] | qh[64] | scales[16] of the block; the block's fp16 d lives
-//         in a separate plane d[row][block] (a 210-byte block cannot sit on a 16-byte boundary)
+//   Q6_K  unit = 208 bytes: ql[128] | qh[64] | scales[16] of the block; the fp16 d of the S blocks
+//         of a stage row follow the row's units (a 210-byte block cannot sit on a 16-byte boundary)
 //   Q8_0  unit = 272 bytes: the 8 x 32 quants of eight consecutive blocks, then their 8 fp16 d
 // The byte count is that of the file in every case; nothing is expanded.
 __host__ __device__ __forceinline__ int gemv_unit_bytes(int type) { return type == T_Q4_K ? 144 : type == T_Q6_K ? 208 : 272; }
 
+// How a [rows][K] matrix of one block type is cut into ring stages. nblk, nslab, S, S_last and R
+// depend on K only, so segments of different types in one launch share them.
+struct GemvGeom {
+  int nblk;      // 256-element blocks per row
+  int nslab;     // stages per tile
+  int S, S_last; // blocks per row in a full stage / in the last stage of a tile
+  int R;         // 16-row groups per tile (> 1 only for short rows, so that all 16 warps have a task)
+  int ub;        // unit bytes
+  int RS, RS_last;        // bytes between rows of a stage (= 32 mod 128)
+  int d_off, d_off_last;  // Q6_K: offset of the row's fp16 block scales within a stage row
+  uint32_t stage_bytes, stage_bytes_last, tile_bytes;
+};
+
+__host__ __device__ __forceinline__ int gemv_pad_row(int bytes) { return (bytes + 95) / 128 * 128 + 32; }
+
+__host__ __device__ inline GemvGeom gemv_geometry(int type, int K) {
+  GemvGeom g;
+  g.nblk = K / 256;
+  g.ub = gemv_unit_bytes(type);
+  g.nslab = (g.nblk + GEMV_WARPS - 1) / GEMV_WARPS;
+  g.S = (g.nblk + g.nslab - 1) / g.nslab;
+  g.S_last = g.nblk - (g.nslab - 1) * g.S;
+  g.R = g.nslab == 1 ? (GEMV_WARPS / g.nblk > 0 ? GEMV_WARPS / g.nblk : 1) : 1;
+  const int dfull = type == T_Q6_K ? (2 * g.S + 15) / 16 * 16 : 0, dlast = type == T_Q6_K ? (2 * g.S_last + 15) / 16 * 16 : 0;
+  g.d_off = g.S * g.ub;
+  g.d_off_last = g.S_last * g.ub;
+  g.RS = gemv_pad_row(g.S * g.ub + dfull);
+  g.RS_last = gemv_pad_row(g.S_last * g.ub + dlast);
+  g.stage_bytes = (uint32_t)(g.R * 16 * g.RS);
+  g.stage_bytes_last = (uint32_t)(g.R * 16 * g.RS_last);
+  g.tile_bytes = (uint32_t)(g.nslab - 1) * g.stage_bytes + g.stage_bytes_last;
+  return g;
+}
+
+// Image row of logical row r. Gate and up projections share one image: every 16-row group holds
+// eight gate rows followed by the same eight up rows (half = 0 gate, 1 up); half < 0: plain.
+__host__ __device__ __forceinline__ int64_t gemv_image_row(int64_t r, int half) {
+  return half < 0 ? r : ((r >> 3) << 4) + (r & 7) + 8 * half;
+}
+
+// Scatters contiguous units [rows][nblk][ub] (and, for Q6_K, their fp16 scales [rows][nblk]) into
+// the stage images. The image must have been zeroed (padding, rows beyond the matrix).
+__global__ void stage_image_kernel(const uint8_t* __restrict__ units, const uint16_t* __restrict__ dsrc, int64_t rows, GemvGeom g,
+                                   int half, uint8_t* __restrict__ img) {
+  const int cpu = g.ub / 16;
+  const int64_t total = rows * g.nblk * cpu;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t u = i / cpu;
+    const int c = (int)(i - u * cpu);
+    const int64_t r = u / g.nblk;
+    const int b = (int)(u - r * g.nblk);
+    const int64_t dr = gemv_image_row(r, half);
+    const int64_t tile = dr / (16 * g.R);
+    const int rr = (int)(dr - tile * 16 * g.R);
+    const int slab = b / g.S, bb = b - slab * g.S;
+    const bool last = slab == g.nslab - 1;
+    uint8_t* dst = img + (size_t)tile * g.tile_bytes + (size_t)slab * g.stage_bytes + (size_t)rr * (last ? g.RS_last : g.RS) +
+                   (size_t)bb * g.ub + (size_t)c * 16;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(units + (size_t)u * g.ub + (size_t)c * 16);
+  }
+  if (dsrc) {
+    const int64_t nd = rows * g.nblk;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < nd; u += stride) {
+      const int64_t r = u / g.nblk;
+      const int b = (int)(u - r * g.nblk);
+      const int64_t dr = gemv_image_row(r, half);
+      const int64_t tile = dr / (16 * g.R);
+      const int rr = (int)(dr - tile * 16 * g.R);
+      const int slab = b / g.S, bb = b - slab * g.S;
+      const bool last = slab == g.nslab - 1;
+      uint8_t* dst = img + (size_t)tile * g.tile_bytes + (size_t)slab * g.stage_bytes + (size_t)rr * (last ? g.RS_last : g.RS) +
+                     (size_t)(last ? g.d_off_last : g.d_off) + (size_t)bb * 2;
+      *reinterpret_cast<uint16_t*>(dst) = dsrc[u];
+    }
+  }
+}
+
 struct GemvSeg {
-  const uint8_t* w;  // units, [rows][K/256][unit]
-  const uint8_t* d;  // Q6_K only: fp16 [rows][K/256]
+  const uint8_t* img;  // stage images, [tiles][tile_bytes]
   int type;
-  int rows;
+  int rows;            // image rows that hold data (SWIGLU: 2 x the projection's rows)
+  int tiles;
+  int RS, RS_last, d_off, d_off_last;
+  uint32_t stage_bytes, stage_bytes_last, tile_bytes;
 };
 
 struct GemvParams {
   GemvSeg seg[3];
   int nseg;
   int K;                // input dimension, a multiple of 256
+  int nblk, nslab, S, S_last, R;  // GemvGeom of K
+  uint32_t slot_bytes;  // ring slot = the largest stage of the launch
   const float* x;       // [batch][x_stride]
   int x_stride;
   const float* norm_w;  // RMSNorm weight fused into the prologue, or nullptr
@@ -77,24 +160,9 @@ struct GemvParams {
   int* amax_idx;
   int amax_row_offset;  // added to the row index reported in amax_idx (vocabulary shard offset)
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
-  int ntiles;           // 16-row tiles (SWIGLU: 8 gate rows + 8 up rows per tile)
-  int slab[3];          // 256-element blocks per row per stage (<= GEMV_SLAB), by format (see gemv_type_index)
-  int row_stride[3];    // bytes between rows of a stage in shared memory (= 32 mod 128), by format
+  int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
 };
-
-__host__ __device__ __forceinline__ int gemv_type_index(int type) { return type == T_Q4_K ? 0 : type == T_Q6_K ? 1 : 2; }
-// Ring geometry per weight format: the widest slab whose 16 padded rows fit one ring slot.
-__host__ __device__ __forceinline__ void gemv_ring_geometry(int K, GemvParams& p) {
-  const int nblk = K / 256;
-  const int ubs[3] = {144, 208, 272};
-  for (int i = 0; i < 3; ++i) {
-    int slab = nblk < GEMV_SLAB ? nblk : GEMV_SLAB;
-    while (slab > 1 && 16 * ((slab * ubs[i] + 127) / 128 * 128 + 32) > GEMV_SLOT_BYTES) --slab;
-    p.slab[i] = slab;
-    p.row_stride[i] = (slab * ubs[i] + 127) / 128 * 128 + 32;
-  }
-}
 
 // ---- shared-memory activation image ------------------------------------------------------
 // planes  [P][plane_stride]   digit bytes, element e of plane p at p*plane_stride + e; the stride
@@ -337,27 +405,58 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 15, %0;" ::"n"(GEMV_WARPS * 32) : "memory"); }
-// split-phase named barrier over the consumer warps: the warps that only contribute partial sums
-// arrive and move on, the warp that finishes the tile waits for all of them
-constexpr int GEMV_TILE_BARS = 8;  // tiles that may be in flight between the fastest and the slowest warp
-__device__ __forceinline__ void tile_bar_arrive(int id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(GEMV_WARPS * 32) : "memory"); }
-__device__ __forceinline__ void tile_bar_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(GEMV_WARPS * 32) : "memory"); }
 
-// ---- per-format work on one 256-element block of a staged 16-row tile ----------------------
-// Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the tile and the k-slice
-// 8t .. 8t+7 of every 32-element group; it receives columns 2t and 2t+1 of the product.
-// pa / pb point at this block's unit in rows g / g + 8 of the stage; L.bplane already includes the lane's 8t offset.
+// ---- per-format work on one 256-element block of a staged 16-row group ----------------------
+// Lane (g = lane >> 2, t = lane & 3) feeds rows g and g + 8 of the group and the k-slice
+// 8t .. 8t+7 of every 32 elements, and supplies column g of the B operand. Column layout:
+//   Q4_K / Q8_0: digit plane p sits in column 2p, so lane t receives plane t in c[0] (row g) and
+//                c[2] (row g + 8); odd columns are zero and c[1], c[3] are ignored;
+//   Q6_K:        a group of 32 elements holds two 16-element sub-blocks; column 2p + s carries
+//                plane p restricted to sub-block s (zero elsewhere), so lane t receives
+//                (plane t, sub-block 0) in c[0] / c[2] and (plane t, sub-block 1) in c[1] / c[3].
 struct LaneCtx {
   int g, t;
-  float wa, wb;    // 256^plane of columns 2t, 2t+1 for Q4_K / Q8_0 (0 for unused columns)
-  float wa6, wb6;  // the same for the Q6_K column layout
-  float wd;        // 256^t: weight of digit t in the minimum / offset terms (t = lane & 3)
-  const uint8_t* bplane;  // digit plane this lane's B column reads (any valid plane for unused columns)
+  float wt;  // 256^t when t < P, else 0: weight of the digit plane this lane receives
+  float wd;  // 256^t: weight of digit t of the activation sums in the minimum / offset terms
+};
+
+// The B operand of one 256-element block for this lane, plus the block's activation sums and scale.
+struct BFrag {
+  uint2 b[8];      // per 32 elements: the two words of column g
+  uint32_t xw[4];  // digit t of the 32-element sums (2 words, Q4_K) or of the 16-element sums (4 words, Q6_K)
+  float sx;
 };
 
 template <int P>
-__device__ __forceinline__ void compute_q4(const uint8_t* pa, const uint8_t* pb, const ActImage& a, int blk, const LaneCtx& L,
-                                           float& acc0, float& acc1) {
+__device__ __forceinline__ void load_bfrag(int type, const ActImage& a, int blk, const LaneCtx& L, BFrag& f) {
+  bool on;
+  int plane;
+  if (type == T_Q6_K) {
+    on = L.g < 2 * P && (L.t >> 1) == (L.g & 1);
+    plane = L.g >> 1;
+  } else {
+    on = !(L.g & 1) && (L.g >> 1) < P;
+    plane = L.g >> 1;
+  }
+  const uint8_t* bp = a.planes + (size_t)(on ? plane : 0) * a.plane_stride + blk * 256 + 8 * L.t;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint2 v = *reinterpret_cast<const uint2*>(bp + 32 * j);
+    f.b[j] = on ? v : make_uint2(0u, 0u);
+  }
+  if (type == T_Q6_K) {
+    const uint4 v = *reinterpret_cast<const uint4*>(a.xs16d + (size_t)L.t * a.n16 + blk * 16);
+    f.xw[0] = v.x; f.xw[1] = v.y; f.xw[2] = v.z; f.xw[3] = v.w;
+  } else {
+    const uint2 v = *reinterpret_cast<const uint2*>(a.xs32d + (size_t)L.t * a.n32 + blk * 8);
+    f.xw[0] = v.x; f.xw[1] = v.y; f.xw[2] = 0u; f.xw[3] = 0u;
+  }
+  f.sx = a.sx[blk];
+}
+
+// pa / pb point at this block's unit in rows g / g + 8 of the stage.
+__device__ __forceinline__ void compute_q4(const uint8_t* pa, const uint8_t* pb, const BFrag& f, const LaneCtx& L, float& acc0,
+                                           float& acc1) {
   const uint4 h0 = *reinterpret_cast<const uint4*>(pa), h1 = *reinterpret_cast<const uint4*>(pb);
   // eight 6-bit scales and minima per row, four to a word (get_scale_min_k4 of the reference,
   // quantization.cpp:145-155, applied to four sub-blocks at once)
@@ -367,138 +466,100 @@ __device__ __forceinline__ void compute_q4(const uint8_t* pa, const uint8_t* pb,
   const uint32_t scA1 = h1.y & 0x3F3F3F3Fu, mnA1 = h1.z & 0x3F3F3F3Fu;
   const uint32_t scB1 = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
   const uint32_t mnB1 = ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u);
-  int Jlo[4] = {0, 0, 0, 0}, Jhi[4] = {0, 0, 0, 0};
-  const uint8_t* bp = L.bplane + blk * 256;
+  int Jlo0 = 0, Jlo1 = 0, Jhi0 = 0, Jhi1 = 0;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const uint2 qa = *reinterpret_cast<const uint2*>(pa + 16 + 32 * c + 8 * L.t), qb = *reinterpret_cast<const uint2*>(pb + 16 + 32 * c + 8 * L.t);
-    const uint2 bl = *reinterpret_cast<const uint2*>(bp + 64 * c), bh = *reinterpret_cast<const uint2*>(bp + 64 * c + 32);
     int cl[4], ch[4];
-    imma_16x8x32<false>(cl, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu, bl.x, bl.y);
-    imma_16x8x32<false>(ch, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u, bh.x, bh.y);  // 16 x
+    imma_16x8x32<false>(cl, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu, f.b[2 * c].x, f.b[2 * c].y);
+    imma_16x8x32<false>(ch, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u, f.b[2 * c + 1].x,
+                        f.b[2 * c + 1].y);  // 16 x the high nibbles
     const uint32_t s0 = c < 2 ? scA0 : scB0, s1 = c < 2 ? scA1 : scB1;
-    const int sl0 = byte_u(s0, (2 * c) & 3), sh0 = byte_u(s0, (2 * c + 1) & 3);
-    const int sl1 = byte_u(s1, (2 * c) & 3), sh1 = byte_u(s1, (2 * c + 1) & 3);
-    Jlo[0] += sl0 * cl[0]; Jlo[1] += sl0 * cl[1]; Jlo[2] += sl1 * cl[2]; Jlo[3] += sl1 * cl[3];
-    Jhi[0] += sh0 * ch[0]; Jhi[1] += sh0 * ch[1]; Jhi[2] += sh1 * ch[2]; Jhi[3] += sh1 * ch[3];
+    Jlo0 += byte_u(s0, (2 * c) & 3) * cl[0];
+    Jlo1 += byte_u(s1, (2 * c) & 3) * cl[2];
+    Jhi0 += byte_u(s0, (2 * c + 1) & 3) * ch[0];
+    Jhi1 += byte_u(s1, (2 * c + 1) & 3) * ch[2];
   }
-  const float f0 = L.wa * fmaf((float)Jhi[0], 0.0625f, (float)Jlo[0]) + L.wb * fmaf((float)Jhi[1], 0.0625f, (float)Jlo[1]);
-  const float f1 = L.wa * fmaf((float)Jhi[2], 0.0625f, (float)Jlo[2]) + L.wb * fmaf((float)Jhi[3], 0.0625f, (float)Jlo[3]);
+  const float f0 = fmaf((float)Jhi0, 0.0625f, (float)Jlo0), f1 = fmaf((float)Jhi1, 0.0625f, (float)Jlo1);
   // minimum term: sum_sub m_sub * X_sub, digit t of X handled by lane t
-  const uint2 xw = *reinterpret_cast<const uint2*>(a.xs32d + (size_t)L.t * a.n32 + blk * 8);
-  const int M0 = dp4a_us(mnB0, xw.y, dp4a_us(mnA0, xw.x, 0));
-  const int M1 = dp4a_us(mnB1, xw.y, dp4a_us(mnA1, xw.x, 0));
-  const float sxb = a.sx[blk];
+  const int M0 = dp4a_us(mnB0, f.xw[1], dp4a_us(mnA0, f.xw[0], 0));
+  const int M1 = dp4a_us(mnB1, f.xw[1], dp4a_us(mnA1, f.xw[0], 0));
   const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&h0.x));
   const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&h1.x));
-  acc0 = fmaf(sxb, dm0.x * f0 - dm0.y * (L.wd * (float)M0), acc0);
-  acc1 = fmaf(sxb, dm1.x * f1 - dm1.y * (L.wd * (float)M1), acc1);
+  acc0 = fmaf(f.sx, dm0.x * (L.wt * f0) - dm0.y * (L.wd * (float)M0), acc0);
+  acc1 = fmaf(f.sx, dm1.x * (L.wt * f1) - dm1.y * (L.wd * (float)M1), acc1);
 }
 
-// Q6_K: a group of 32 consecutive elements holds two 16-element sub-blocks. Lanes t = 0,1 carry
-// the first one, t = 2,3 the second; columns 0..P-1 see only the first (B is zero for t >= 2),
-// columns P..2P-1 only the second, so one instruction yields both sub-block sums separately.
-template <int P>
-__device__ __forceinline__ void compute_q6(const uint8_t* pa, const uint8_t* pb, float d0, float d1, const ActImage& a, int blk,
-                                           const LaneCtx& L, float& acc0, float& acc1) {
-  const int col = L.g, sub_of_col = col / P, plane = col - sub_of_col * P;
-  const bool b_on = col < 2 * P && sub_of_col == (L.t >> 1);
-  const uint32_t selA = (uint32_t)((2 * L.t) / P), selB = (uint32_t)((2 * L.t + 1) / P);
-  const uint8_t* bp = a.planes + (size_t)(b_on ? plane : 0) * a.plane_stride + blk * 256 + 8 * L.t;
+__device__ __forceinline__ void compute_q6(const uint8_t* pa, const uint8_t* pb, float d0, float d1, const BFrag& f, const LaneCtx& L,
+                                           float& acc0, float& acc1) {
   const uint4 sc0 = *reinterpret_cast<const uint4*>(pa + 192), sc1 = *reinterpret_cast<const uint4*>(pb + 192);
-  int J[4] = {0, 0, 0, 0};
+  const uint32_t sw0[4] = {sc0.x, sc0.y, sc0.z, sc0.w}, sw1[4] = {sc1.x, sc1.y, sc1.z, sc1.w};
+  int J0 = 0, J1 = 0;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint2 ha = *reinterpret_cast<const uint2*>(pa + 128 + 32 * h + 8 * L.t), hb = *reinterpret_cast<const uint2*>(pb + 128 + 32 * h + 8 * L.t);
-    const uint32_t hw[2][2] = {{ha.x, ha.y}, {hb.x, hb.y}};
 #pragma unroll
-    for (int g4 = 0; g4 < 4; ++g4) {
-      uint32_t av[2][2];
+    for (int q = 0; q < 2; ++q) {
+      const uint2 la = *reinterpret_cast<const uint2*>(pa + 64 * h + 32 * q + 8 * L.t), lb = *reinterpret_cast<const uint2*>(pb + 64 * h + 32 * q + 8 * L.t);
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint2 lw = *reinterpret_cast<const uint2*>((i ? pb : pa) + 64 * h + 32 * (g4 & 1) + 8 * L.t);
-        const uint32_t l2[2] = {lw.x, lw.y};
-#pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          const uint32_t nib = g4 < 2 ? (l2[w] & 0x0F0F0F0Fu) : ((l2[w] >> 4) & 0x0F0F0F0Fu);
-          const uint32_t hi = g4 == 0 ? (hw[i][w] << 4) : g4 == 1 ? (hw[i][w] << 2) : g4 == 2 ? hw[i][w] : (hw[i][w] >> 2);
-          av[i][w] = nib | (hi & 0x30303030u);
-        }
+      for (int hi = 0; hi < 2; ++hi) {
+        const int g4 = q + 2 * hi;  // 32-element group within the 128-element half (reference quantization.cpp:223-266)
+        auto six = [&](uint32_t lw, uint32_t hw) -> uint32_t {
+          const uint32_t nib = hi ? ((lw >> 4) & 0x0F0F0F0Fu) : (lw & 0x0F0F0F0Fu);
+          const uint32_t top = g4 == 0 ? (hw << 4) : g4 == 1 ? (hw << 2) : g4 == 2 ? hw : (hw >> 2);
+          return nib | (top & 0x30303030u);
+        };
+        int c[4];
+        imma_16x8x32<false>(c, six(la.x, ha.x), six(lb.x, hb.x), six(la.y, ha.y), six(lb.y, hb.y), f.b[4 * h + g4].x, f.b[4 * h + g4].y);
+        // sub-block 8h + 2*g4 + s: byte 2*(g4 & 1) + s of scale word 2h + g4/2
+        const uint32_t w0 = sw0[2 * h + hi], w1 = sw1[2 * h + hi];
+        J0 += byte_s(w0, 2 * q) * c[0];
+        J0 += byte_s(w0, 2 * q + 1) * c[1];
+        J1 += byte_s(w1, 2 * q) * c[2];
+        J1 += byte_s(w1, 2 * q + 1) * c[3];
       }
-      uint2 bv = *reinterpret_cast<const uint2*>(bp + 128 * h + 32 * g4);
-      if (!b_on) bv = make_uint2(0u, 0u);
-      int c[4];
-      imma_16x8x32<false>(c, av[0][0], av[1][0], av[0][1], av[1][1], bv.x, bv.y);
-      // sub-scale index within the block: 8h + 2*g4 + (0|1) -> word (2h + g4/2), byte 2(g4&1) + sel
-      const int wsel = 2 * h + (g4 >> 1);
-      const uint32_t w0 = wsel == 0 ? sc0.x : wsel == 1 ? sc0.y : wsel == 2 ? sc0.z : sc0.w;
-      const uint32_t w1 = wsel == 0 ? sc1.x : wsel == 1 ? sc1.y : wsel == 2 ? sc1.z : sc1.w;
-      const uint32_t bA = 2 * (g4 & 1) + selA, bB = 2 * (g4 & 1) + selB;
-      J[0] += byte_s(w0, bA) * c[0];
-      J[1] += byte_s(w0, bB) * c[1];
-      J[2] += byte_s(w1, bA) * c[2];
-      J[3] += byte_s(w1, bB) * c[3];
     }
   }
-  const float f0 = L.wa6 * (float)J[0] + L.wb6 * (float)J[1];
-  const float f1 = L.wa6 * (float)J[2] + L.wb6 * (float)J[3];
   // offset term: the stored quants are q + 32, so subtract 32 * sum_sub sc_sub * X_sub (digit t per lane)
-  const uint4 xw = *reinterpret_cast<const uint4*>(a.xs16d + (size_t)L.t * a.n16 + blk * 16);
-  const int C0 = dp4a_ss(sc0.w, xw.w, dp4a_ss(sc0.z, xw.z, dp4a_ss(sc0.y, xw.y, dp4a_ss(sc0.x, xw.x, 0))));
-  const int C1 = dp4a_ss(sc1.w, xw.w, dp4a_ss(sc1.z, xw.z, dp4a_ss(sc1.y, xw.y, dp4a_ss(sc1.x, xw.x, 0))));
-  const float sxb = a.sx[blk];
-  acc0 = fmaf(sxb * d0, f0 - 32.f * (L.wd * (float)C0), acc0);
-  acc1 = fmaf(sxb * d1, f1 - 32.f * (L.wd * (float)C1), acc1);
+  const int C0 = dp4a_ss(sc0.w, f.xw[3], dp4a_ss(sc0.z, f.xw[2], dp4a_ss(sc0.y, f.xw[1], dp4a_ss(sc0.x, f.xw[0], 0))));
+  const int C1 = dp4a_ss(sc1.w, f.xw[3], dp4a_ss(sc1.z, f.xw[2], dp4a_ss(sc1.y, f.xw[1], dp4a_ss(sc1.x, f.xw[0], 0))));
+  acc0 = fmaf(f.sx * d0, L.wt * (float)J0 - 32.f * (L.wd * (float)C0), acc0);
+  acc1 = fmaf(f.sx * d1, L.wt * (float)J1 - 32.f * (L.wd * (float)C1), acc1);
 }
 
-template <int P>
-__device__ __forceinline__ void compute_q8(const uint8_t* pa, const uint8_t* pb, const ActImage& a, int blk, const LaneCtx& L,
-                                           float& acc0, float& acc1) {
+__device__ __forceinline__ void compute_q8(const uint8_t* pa, const uint8_t* pb, const BFrag& f, const LaneCtx& L, float& acc0,
+                                           float& acc1) {
   const uint4 da = *reinterpret_cast<const uint4*>(pa + 256), db = *reinterpret_cast<const uint4*>(pb + 256);
   const uint32_t dw0[4] = {da.x, da.y, da.z, da.w}, dw1[4] = {db.x, db.y, db.z, db.w};
-  const uint8_t* bp = L.bplane + blk * 256;
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const uint2 qa = *reinterpret_cast<const uint2*>(pa + 32 * j + 8 * L.t), qb = *reinterpret_cast<const uint2*>(pb + 32 * j + 8 * L.t);
-    const uint2 bv = *reinterpret_cast<const uint2*>(bp + 32 * j);
     int c[4];
-    imma_16x8x32<true>(c, qa.x, qb.x, qa.y, qb.y, bv.x, bv.y);
+    imma_16x8x32<true>(c, qa.x, qb.x, qa.y, qb.y, f.b[j].x, f.b[j].y);
     // the scale field of a Q8_0 block is used by magnitude (reference quantization.cpp:85-87)
     const float d0 = scale_field_to_float((uint16_t)((dw0[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
     const float d1 = scale_field_to_float((uint16_t)((dw1[j >> 1] >> (16 * (j & 1))) & 0xFFFF));
-    s0 = fmaf(d0, L.wa * (float)c[0] + L.wb * (float)c[1], s0);
-    s1 = fmaf(d1, L.wa * (float)c[2] + L.wb * (float)c[3], s1);
+    s0 = fmaf(d0, (float)c[0], s0);
+    s1 = fmaf(d1, (float)c[2], s1);
   }
-  const float sxb = a.sx[blk];
-  acc0 = fmaf(sxb, s0, acc0);
-  acc1 = fmaf(sxb, s1, acc1);
+  acc0 = fmaf(f.sx * L.wt, s0, acc0);
+  acc1 = fmaf(f.sx * L.wt, s1, acc1);
 }
 
-// Maps (tile, row-in-tile 0..15) to a segment and a row of it. Ordinary launches: the segments'
-// rows are concatenated and cut into 16-row tiles (every segment but the last has a multiple of
-// 16 rows). SwiGLU launches: tile = 8 rows of seg 0 (gate) followed by the same 8 rows of seg 1 (up).
-__device__ __forceinline__ void tile_row(const GemvParams& p, int tile, int r, int& seg, int& row, bool& valid) {
-  if (p.epi == EPI_SWIGLU) {
-    seg = r >> 3;
-    row = tile * 8 + (r & 7);
-    valid = row < p.seg[0].rows;
-  } else {
-    row = tile * 16 + r;
-    seg = 0;
-    while (seg + 1 < p.nseg && row >= p.seg[seg].rows) { row -= p.seg[seg].rows; ++seg; }
-    valid = row < p.seg[seg].rows;
-  }
-  if (!valid) row = p.seg[seg].rows - 1;  // loads stay in bounds; the result is discarded
+// Segment and tile-within-segment of a launch-wide tile index (segments are laid end to end).
+__device__ __forceinline__ void gemv_locate(const GemvParams& p, int tile, int& seg, int& tl) {
+  seg = 0;
+  tl = tile;
+  while (seg + 1 < p.nseg && tl >= p.seg[seg].tiles) { tl -= p.seg[seg].tiles; ++seg; }
 }
-
 
 // ---- the streaming pipeline ----------------------------------------------------------------
 struct GemvShared {
   unsigned long long full_bar[GEMV_MAX_STAGES];
   unsigned long long empty_bar[GEMV_MAX_STAGES];
   float red[GEMV_WARPS + 2];
-  float part[GEMV_TILE_BARS][GEMV_WARPS][16];
+  float part[GEMV_NTB][GEMV_WARPS][16];
   float sv[GEMV_WARPS];
   int si[GEMV_WARPS];
   int abort_flag;
@@ -507,11 +568,10 @@ struct GemvShared {
 struct PipeCtx {
   GemvShared* sh;
   uint8_t* act;   // activation image
-  uint8_t* ring;  // nstages slots of GEMV_SLOT_BYTES
+  uint8_t* ring;  // nstages slots of slot_bytes
   int nstages;
   int slot;       // ring slot of the next stage (producer and consumers count alike)
   int use;        // how many times the ring has wrapped
-  int gt;         // tiles finished so far
   __device__ __forceinline__ void next_stage() {
     if (++slot == nstages) { slot = 0; ++use; }
   }
@@ -520,7 +580,7 @@ struct PipeCtx {
 __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < nstages; ++s) {
-      mbar_init(&sh->full_bar[s], GEMV_PROD_WARPS);
+      mbar_init(&sh->full_bar[s], 1);
       mbar_init(&sh->empty_bar[s], GEMV_WARPS);
     }
     sh->abort_flag = 0;
@@ -534,129 +594,59 @@ __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh)
   if (prm.error_flag) atomicExch(prm.error_flag, 1);
 }
 
-// Producer warp pw (0..3): lanes 0..3 copy rows 4*pw .. 4*pw+3 of every stage of this CTA's tiles.
-__device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int pw, int lane, int cta, int ncta) {
+// The producer (one thread): one bulk copy per stage of this CTA's tiles. Tiles are dealt
+// round-robin over the CTAs so that launches mixing formats of different cost stay balanced.
+__device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int cta, int ncta) {
   GemvShared* sh = pc.sh;
-  const int nblk = prm.K / 256;
-  // tiles are dealt round-robin over the CTAs so that launches mixing formats of different cost
-  // (Q6_K tiles take about twice as long as Q4_K ones) stay balanced
   for (int tile = cta; tile < prm.ntiles; tile += ncta) {
-    int seg = 0, row = 0;
-    bool valid;
-    tile_row(prm, tile, 4 * pw + (lane & 3), seg, row, valid);
-    const int type = prm.seg[seg].type, ti = gemv_type_index(type);
-    const int ub = gemv_unit_bytes(type);
-    const int slab_blocks = prm.slab[ti], RSS = prm.row_stride[ti];
-    const int nslab = (nblk + slab_blocks - 1) / slab_blocks;
-    const uint8_t* src_row = prm.seg[seg].w + (size_t)row * nblk * ub;
-    for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
+    int s, tl;
+    gemv_locate(prm, tile, s, tl);
+    const GemvSeg& sg = prm.seg[s];
+    const uint8_t* src = sg.img + (size_t)tl * sg.tile_bytes;
+    for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
       const int slot = pc.slot, use = pc.use;
-      if (use > 0) {
-        if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
-        __syncwarp();
-      }
-      const int b0 = slab * slab_blocks, nb = min(slab_blocks, nblk - b0);
-      const uint32_t bytes = (uint32_t)(nb * ub);
-      if (lane == 0) mbar_expect_tx(&sh->full_bar[slot], bytes * 4);
-      __syncwarp();
-      if (lane < 4)
-        bulk_g2s(pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)(4 * pw + lane) * RSS, src_row + (size_t)b0 * ub, bytes,
-                 &sh->full_bar[slot]);
+      if (use > 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
+      const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
+      mbar_expect_tx(&sh->full_bar[slot], bytes);
+      bulk_g2s(pc.ring + (size_t)slot * prm.slot_bytes, src + (size_t)slab * sg.stage_bytes, bytes, &sh->full_bar[slot]);
     }
   }
 }
 
-// The 16 consumer warps: prologue, then one block column per warp per stage, then the row epilogue.
-template <int P, typename XFN>
-__device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc, XFN xfn, int bidx, int cta, int ncta, float& best_v,
-                                             int& best_i) {
-  GemvShared* sh = pc.sh;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red);
-  const ActImage a = act_carve(pc.act, prm.K, P);
-
-  LaneCtx L;
-  L.g = lane >> 2;
-  L.t = lane & 3;
-  {
-    const int c0 = 2 * L.t, c1 = 2 * L.t + 1;
-    auto p256 = [](int e) { return __int_as_float((127 + 8 * e) << 23); };  // 256^e
-    L.wa = c0 < P ? p256(c0) : 0.f;
-    L.wb = c1 < P ? p256(c1) : 0.f;
-    L.wa6 = c0 < 2 * P ? p256(c0 % P) : 0.f;
-    L.wb6 = c1 < 2 * P ? p256(c1 % P) : 0.f;
-    L.wd = p256(L.t);
-    L.bplane = a.planes + (size_t)(L.g < P ? L.g : 0) * a.plane_stride + 8 * L.t;
-  }
-  const int nblk = prm.K / 256;
-
-  for (int tile = cta; tile < prm.ntiles; tile += ncta, ++pc.gt) {
-    int segA, rowA, segB, rowB;
-    bool vA, vB;
-    tile_row(prm, tile, L.g, segA, rowA, vA);
-    tile_row(prm, tile, L.g + 8, segB, rowB, vB);
-    const int type = prm.seg[segA].type, ti = gemv_type_index(type);
-    const int ub = gemv_unit_bytes(type);
-    const int slab_blocks = prm.slab[ti], RSS = prm.row_stride[ti];
-    const int nslab = (nblk + slab_blocks - 1) / slab_blocks;
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int slab = 0; slab < nslab; ++slab, pc.next_stage()) {
-      const int slot = pc.slot, use = pc.use;
-      const int b0 = slab * slab_blocks, nb = min(slab_blocks, nblk - b0);
-      const int blk = b0 + warp;
-      float d0 = 0.f, d1 = 0.f;
-      if (type == T_Q6_K && warp < nb) {  // requested before the wait so its latency hides behind it
-        d0 = half_bits_to_float(ldg16(prm.seg[segA].d + ((size_t)rowA * nblk + blk) * 2));
-        d1 = half_bits_to_float(ldg16(prm.seg[segB].d + ((size_t)rowB * nblk + blk) * 2));
-      }
-      if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->full_bar[slot], use & 1)) pipe_fail(prm, sh);
-      __syncwarp();  // one lane probes; the rest of the warp parks here
-      if (warp < nb) {
-        const uint8_t* pa = pc.ring + (size_t)slot * GEMV_SLOT_BYTES + (size_t)L.g * RSS + (size_t)warp * ub;
-        const uint8_t* pb = pa + (size_t)8 * RSS;
-        if (type == T_Q4_K) compute_q4<P>(pa, pb, a, blk, L, acc0, acc1);
-        else if (type == T_Q6_K) compute_q6<P>(pa, pb, d0, d1, a, blk, L, acc0, acc1);
-        else compute_q8<P>(pa, pb, a, blk, L, acc0, acc1);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->empty_bar[slot]);
-    }
-    // ---- tile finished: fold the four k-slices, hand the partial sums to the finishing warp ----
-    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    // A warp can run at most nstages (< GEMV_TILE_BARS) tiles ahead of the slowest one, so slot and
-    // barrier gt % GEMV_TILE_BARS are free again when they come round.
-    const int pp = pc.gt % GEMV_TILE_BARS;
-    if (L.t == 0) {
-      sh->part[pp][warp][L.g] = acc0;
-      sh->part[pp][warp][L.g + 8] = acc1;
-    }
-    if (warp != (pc.gt & (GEMV_WARPS - 1))) {
-      __syncwarp();
-      tile_bar_arrive(1 + pp);
-      continue;
-    }
-    tile_bar_sync(1 + pp);  // this warp finishes the tile; lanes 0..15 own one row each
-    const int r = lane & 15;
+// Finishes the rows of the n tiles parked in sh->part (tiles first_i .. first_i+n-1 of this CTA's
+// sequence): every thread sums the partials of one row in warp order and applies the epilogue.
+__device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh, int first_i, int n, int bidx, int cta, int ncta,
+                                           float& best_v, int& best_i) {
+  consumer_sync();
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int R = prm.R, S = prm.S;
+  const int total = n * R * 16;
+  for (int base = (tid & ~31); base < total; base += GEMV_WARPS * 32) {
+    const int idx = base + lane;
+    const bool in = idx < total;
+    const int slot = in ? idx / (16 * R) : 0;
+    const int rgi = in ? (idx >> 4) - slot * R : 0;
+    const int r = idx & 15;
     float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < GEMV_WARPS; ++w) tot += sh->part[pp][w][r];
+    if (in) {
+      const float* pp = &sh->part[slot][rgi * S][r];
+      for (int s = 0; s < S; ++s) tot += pp[s * 16];
+    }
+    int seg, tl;
+    gemv_locate(prm, cta + (first_i + slot) * ncta, seg, tl);
+    const int irow = (tl * R + rgi) * 16 + r;  // image row within the segment
+    const bool valid = in && irow < prm.seg[seg].rows;
     if (prm.epi == EPI_SWIGLU) {
       // reference model.cpp:734-735 with silu_cpu (utils.cpp:700-707): (g * 1/(1+exp(-g))) * u
-      const float u = __shfl_sync(0xffffffffu, tot, (lane & 7) + 8);
-      const int row = tile * 8 + (lane & 7);
-      if (lane < 8 && row < prm.seg[0].rows) {
+      const float u = __shfl_sync(0xffffffffu, tot, (lane & 23) + 8);
+      if (valid && r < 8) {
         const float sig = 1.0f / (1.0f + expf(-tot));
-        prm.y[(size_t)bidx * prm.y_stride + row] = (tot * sig) * u;
+        prm.y[(size_t)bidx * prm.y_stride + (irow >> 4) * 8 + r] = (tot * sig) * u;
       }
     } else {
-      int seg, row;
-      bool valid;
-      tile_row(prm, tile, r, seg, row, valid);
       const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
-      if (lane < 16 && valid) {
+      if (valid) {
+        const int row = irow;
         if (prm.epi == EPI_RESID) {
           const float* rs = (prm.resid ? prm.resid : prm.y) + (size_t)bidx * prm.y_stride + row;
           prm.y[(size_t)bidx * prm.y_stride + row] = *rs + tot;
@@ -682,9 +672,84 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
       }
     }
   }
+  consumer_sync();
 }
 
-// Per-CTA (value, first index) of the rows this CTA produced, from the per-lane running bests.
+// The 16 consumer warps: prologue, then one (row group, block) task per warp per stage; the rows
+// are finished GEMV_NTB tiles at a time.
+template <int P, bool BREG, typename XFN>
+__device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc, XFN xfn, int bidx, int cta, int ncta, float& best_v,
+                                             int& best_i) {
+  GemvShared* sh = pc.sh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red);
+  const ActImage a = act_carve(pc.act, prm.K, P);
+
+  LaneCtx L;
+  L.g = lane >> 2;
+  L.t = lane & 3;
+  L.wd = __int_as_float((127 + 8 * L.t) << 23);  // 256^t
+  L.wt = L.t < P ? L.wd : 0.f;
+  const int rg = warp / prm.S, bi = warp - rg * prm.S;  // this warp's row group and block within a stage
+  const bool rg_ok = rg < prm.R;
+  BFrag bf;
+  int cur_type = -1;
+
+  int i = 0;
+  for (int tile = cta; tile < prm.ntiles; tile += ncta, ++i) {
+    int s, tl;
+    gemv_locate(prm, tile, s, tl);
+    const GemvSeg& sg = prm.seg[s];
+    const int type = sg.type;
+    const int ub = gemv_unit_bytes(type);
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
+      const int slot = pc.slot, use = pc.use;
+      const bool last = slab == prm.nslab - 1;
+      const bool active = rg_ok && bi < (last ? prm.S_last : prm.S);
+      // the activation digits are ready before the weights: fetch them ahead of the wait (with at
+      // most 16 blocks per row the warp meets the same block every time and keeps them)
+      if (active && (!BREG || type != cur_type)) {
+        load_bfrag<P>(type, a, slab * prm.S + bi, L, bf);
+        cur_type = type;
+      }
+      if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->full_bar[slot], use & 1)) pipe_fail(prm, sh);
+      __syncwarp();  // one lane probes; the rest of the warp parks here
+      if (active) {
+        const int RSt = last ? sg.RS_last : sg.RS;
+        const uint8_t* ra = pc.ring + (size_t)slot * prm.slot_bytes + (size_t)(rg * 16 + L.g) * RSt;
+        const uint8_t* pa = ra + bi * ub;
+        const uint8_t* pb = pa + 8 * RSt;
+        if (type == T_Q4_K) {
+          compute_q4(pa, pb, bf, L, acc0, acc1);
+        } else if (type == T_Q6_K) {
+          const int dof = (last ? sg.d_off_last : sg.d_off) + 2 * bi;
+          const float d0 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(ra + dof));
+          const float d1 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(ra + 8 * RSt + dof));
+          compute_q6(pa, pb, d0, d1, bf, L, acc0, acc1);
+        } else {
+          compute_q8(pa, pb, bf, L, acc0, acc1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->empty_bar[slot]);
+    }
+    // ---- tile finished: fold the four k-slices and park the partial sums ----
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    const int pp = i % GEMV_NTB;
+    if (L.t == 0) {
+      sh->part[pp][warp][L.g] = acc0;
+      sh->part[pp][warp][L.g + 8] = acc1;
+    }
+    if (pp == GEMV_NTB - 1) gemv_flush(prm, sh, i - pp, GEMV_NTB, bidx, cta, ncta, best_v, best_i);
+  }
+  if (i % GEMV_NTB) gemv_flush(prm, sh, i - i % GEMV_NTB, i % GEMV_NTB, bidx, cta, ncta, best_v, best_i);
+}
+
+// Per-CTA (value, first index) of the rows this CTA produced, from the per-thread running bests.
 __device__ __forceinline__ void gemv_store_argmax(const GemvParams& prm, GemvShared* sh, float best_v, int best_i, int bidx, int cta,
                                                   int ncta) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -717,7 +782,8 @@ struct XFromGlobal {
 };
 
 // One launch = one fused matvec for blockIdx.y's activation vector; one persistent CTA per SM.
-template <int P>
+// BREG: rows have at most 16 blocks (one stage per tile), so B fragments stay in registers.
+template <int P, bool BREG>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm, int nstages) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ GemvShared sh;
@@ -728,20 +794,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
   pc.nstages = nstages;
   pc.slot = 0;
   pc.use = 0;
-  pc.gt = 0;
   pipe_init(&sh, nstages);
   pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   if (warp >= GEMV_WARPS) {
-    // weights never depend on the previous kernel, so the producers start before the consumers' dependency wait
-    gemv_produce(prm, pc, warp - GEMV_WARPS, lane, blockIdx.x, gridDim.x);
+    // weights never depend on the previous kernel, so the producer starts before the consumers' dependency wait
+    if (threadIdx.x == GEMV_WARPS * 32) gemv_produce(prm, pc, blockIdx.x, gridDim.x);
     return;
   }
   pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
-  gemv_consume<P>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
+  gemv_consume<P, BREG>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
   if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
 }
 
