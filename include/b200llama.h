@@ -128,7 +128,7 @@ int b200_attention_decode(const float* q, const float* k_new, const float* v_new
  * position = one int, the index of the new token (rows 0..position-1 of the caches are read, row
  * `position` is written); out [n_heads][hd]. The split-K scratch is a fixed array inside the library
  * (about 1 MiB per GPU, held until the process exits): n_heads * n_splits <= 2048, n_heads <= 512,
- * head_dim <= 128, anything larger is refused with status 2 and a message. The first call on each
+ * n_splits <= 64, head_dim <= 128, anything larger is refused with status 2 and a message. The first call on each
  * device looks up that array's address and raises the kernel's shared-memory limit; make that call
  * outside any stream capture. Calls share the scratch, so two calls whose kernels overlap on the GPU
  * (different streams) race; calls on one stream are safe. The launch is asynchronous on `stream`

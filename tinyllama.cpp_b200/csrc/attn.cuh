@@ -6,9 +6,8 @@
 // kv head) absmax scale: scale = absmax/127, or 1 when absmax <= 1e-8; q = clamp(roundf(x/scale),
 // -127, 127) — the arithmetic of the reference quantizer, cuda_kernels.cu:1535-1549 and 1596-1599)
 // and written to the cache by the first query head of the group. Partial (max, sum, output)
-// triples go to a scratch buffer and are merged in split order, so the result does not depend on
-// scheduling: either by the last group of a head to finish (atomic ticket; stand-alone kernel) or
-// by whoever consumes the attention output next (persistent kernel).
+// triples go to a scratch buffer and are merged in split order by the last group of a head to
+// finish (atomic ticket), so the result does not depend on scheduling.
 //
 // Softmax follows the reference CPU code (model.cpp:632-663, utils.cpp:675-698):
 //   s_t = (q . k_t) / sqrt(hd);  p_t = exp(s_t - max);  o = sum p_t v_t / (sum p_t + 1e-9).
@@ -53,22 +52,41 @@ __host__ __device__ __forceinline__ size_t attn_group_floats(int hd, int max_ctx
   return (size_t)(3 * hd + 4 * hd + attn_split_cap(max_ctx, nsplit) + 16);
 }
 
-// Merges the per-split partials of (sequence b, head h) in split order.
-__device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, int h, int gtid, int nthr, float* dst) {
+constexpr int ATTN_MAX_SPLITS = 64;
+
+// Merges the per-split partials of (sequence b, head h) in split order. All loads of a phase are
+// issued together (one L2 round trip for the (max, sum) pairs, one for the partial outputs)
+// instead of one dependent load per split. scratch: 3 * ATTN_MAX_SPLITS floats of shared memory;
+// called by all nthr threads of the group, which synchronise on bar_id.
+__device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, int h, int gtid, int nthr, float* dst, float* scratch,
+                                                int bar_id) {
   const size_t pbase = ((size_t)b * prm.nq + h) * prm.nsplit;
-  float M = -INFINITY;
-  for (int s = 0; s < prm.nsplit; ++s) M = fmaxf(M, __ldcg(&prm.part_ml[(pbase + s) * 2]));
-  float L = 0.f;
-  for (int s = 0; s < prm.nsplit; ++s) {
-    const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
-    if (ls > 0.f) L += ls * expf(ms - M);
+  float* m_s = scratch;
+  float* l_s = scratch + ATTN_MAX_SPLITS;
+  float* w_s = scratch + 2 * ATTN_MAX_SPLITS;
+  if (gtid < prm.nsplit) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&prm.part_ml[(pbase + gtid) * 2]));
+    m_s[gtid] = ml.x;
+    l_s[gtid] = ml.y;
   }
+  group_sync(bar_id);
+  float M = -INFINITY;
+  for (int s = 0; s < prm.nsplit; ++s) M = fmaxf(M, m_s[s]);
+  if (gtid < prm.nsplit) w_s[gtid] = l_s[gtid] > 0.f ? expf(m_s[gtid] - M) : 0.f;
+  group_sync(bar_id);
+  float L = 0.f;
+  for (int s = 0; s < prm.nsplit; ++s)
+    if (l_s[s] > 0.f) L += l_s[s] * w_s[s];
   const float inv = 1.0f / (L + 1e-9f);
   for (int d = gtid; d < prm.hd; d += nthr) {
     float o = 0.f;
-    for (int s = 0; s < prm.nsplit; ++s) {
-      const float ms = __ldcg(&prm.part_ml[(pbase + s) * 2]), ls = __ldcg(&prm.part_ml[(pbase + s) * 2 + 1]);
-      if (ls > 0.f) o = fmaf(expf(ms - M), __ldcg(&prm.part_o[(pbase + s) * prm.hd + d]), o);
+    for (int s0 = 0; s0 < prm.nsplit; s0 += 16) {  // sixteen loads in flight at a time
+      float v[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s) v[s] = s0 + s < prm.nsplit ? __ldcg(&prm.part_o[(pbase + s0 + s) * prm.hd + d]) : 0.f;
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s0 + s < prm.nsplit) o = fmaf(w_s[s0 + s], v[s], o);
     }
     dst[d] = o * inv;
   }
@@ -272,7 +290,7 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
 
 // Stand-alone kernel: one group per CTA, ticket merge by the last CTA of each (sequence, head).
 template <bool KV_I8>
-__global__ void __launch_bounds__(ATTN_GROUP_THREADS) attn_decode_kernel(const AttnParams prm) {
+__global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(const AttnParams prm) {
   extern __shared__ __align__(16) float sm[];
   __shared__ int last_flag;
   // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
@@ -291,7 +309,7 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS) attn_decode_kernel(const A
   }
   __syncthreads();
   if (!last_flag) return;
-  attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd);
+  attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd, sm, 1);
   if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
 }
 

@@ -202,14 +202,9 @@ __device__ __forceinline__ ActImage act_carve(uint8_t* smem, int K, int P) {
 
 __device__ __forceinline__ void consumer_sync();
 
-// balanced base-256 digits of v: v = d0 + 256 d1 + 65536 d2 + 2^24 d3, every d in [-128, 127]
-__device__ __forceinline__ void balanced_digits4(int v, int (&d)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    d[i] = (int)(int8_t)(v & 0xFF);
-    v = (v - d[i]) >> 8;
-  }
-}
+// Balanced base-256 digits (every digit a signed byte in [-128, 127]) come from plain byte
+// extraction after a bias: v + 0x80...80 has bytes digit + 128, and xor 0x80 turns them into the
+// signed digits.
 
 // Quantises the eight elements v[] this lane holds of 256-element block b (after the optional
 // RMSNorm scaling) and writes the block's digit planes, digit sums and scale.
@@ -222,6 +217,7 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
   uint8_t* xs16d = const_cast<uint8_t*>(a.xs16d);
   // largest magnitude P balanced digits can hold: 127 * (256^P - 1) / 255
   constexpr int QMAX = P == 3 ? 8355711 : (P == 2 ? 32639 : 127);
+  constexpr int BIAS = P == 3 ? 0x808080 : (P == 2 ? 0x8080 : 0x80);
   const int e0 = b * 256 + lane * 8;
   float v[8];
 #pragma unroll
@@ -238,37 +234,32 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
   const float scale = amax / (float)QMAX;
   const float inv = amax > 0.f ? (float)QMAX / amax : 0.f;
   int s8 = 0;
-  uint32_t pw[P][2];
-#pragma unroll
-  for (int p = 0; p < P; ++p) pw[p][0] = pw[p][1] = 0;
+  uint32_t u[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     int q = __float2int_rn(v[i] * inv);
     q = max(-QMAX, min(QMAX, q));
     s8 += q;
-#pragma unroll
-    for (int p = 0; p < P; ++p) {
-      const int dgt = (int)(int8_t)(q & 0xFF);
-      q = (q - dgt) >> 8;
-      pw[p][i >> 2] |= (uint32_t)(dgt & 0xFF) << (8 * (i & 3));
-    }
+    u[i] = (uint32_t)(q + BIAS);
   }
 #pragma unroll
-  for (int p = 0; p < P; ++p)
-    *reinterpret_cast<uint2*>(planes + (size_t)p * a.plane_stride + e0) = make_uint2(pw[p][0], pw[p][1]);
+  for (int p = 0; p < P; ++p) {
+    const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);  // byte p of the first word, byte p of the second
+    const uint32_t w0 = __byte_perm(__byte_perm(u[0], u[1], sel), __byte_perm(u[2], u[3], sel), 0x5410) ^ 0x80808080u;
+    const uint32_t w1 = __byte_perm(__byte_perm(u[4], u[5], sel), __byte_perm(u[6], u[7], sel), 0x5410) ^ 0x80808080u;
+    *reinterpret_cast<uint2*>(planes + (size_t)p * a.plane_stride + e0) = make_uint2(w0, w1);
+  }
   const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
   const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
   if ((lane & 1) == 0) {
-    int dg[4];
-    balanced_digits4(s16, dg);
+    const uint32_t dg = ((uint32_t)s16 + 0x80808080u) ^ 0x80808080u;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) xs16d[i * a.n16 + b * 16 + (lane >> 1)] = (uint8_t)dg[i];
+    for (int i = 0; i < 4; ++i) xs16d[i * a.n16 + b * 16 + (lane >> 1)] = (uint8_t)(dg >> (8 * i));
   }
   if ((lane & 3) == 0) {
-    int dg[4];
-    balanced_digits4(s32, dg);
+    const uint32_t dg = ((uint32_t)s32 + 0x80808080u) ^ 0x80808080u;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) xs32d[i * a.n32 + b * 8 + (lane >> 2)] = (uint8_t)dg[i];
+    for (int i = 0; i < 4; ++i) xs32d[i * a.n32 + b * 8 + (lane >> 2)] = (uint8_t)(dg >> (8 * i));
   }
   if (lane == 0) sx[b] = scale;
 }
@@ -314,10 +305,16 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
     consumer_sync();
-    double t = 0.0;
+    // fixed-order pairwise sum of the 16 warp partials (the reference accumulates in double; FP64
+    // on this part costs more than a microsecond here and the difference is below 1e-7 relative)
+    float r[GEMV_WARPS];
 #pragma unroll
-    for (int w = 0; w < GEMV_WARPS; ++w) t += (double)red[w];
-    f = 1.0f / sqrtf((float)(t / (double)K) + eps);
+    for (int w = 0; w < GEMV_WARPS; ++w) r[w] = red[w];
+#pragma unroll
+    for (int n = GEMV_WARPS / 2; n > 0; n >>= 1)
+#pragma unroll
+      for (int w = 0; w < n; ++w) r[w] = r[2 * w] + r[2 * w + 1];
+    f = 1.0f / sqrtf(r[0] / (float)K + eps);
   }
   const ActImage a = act_carve(smem, K, P);
 #pragma unroll
