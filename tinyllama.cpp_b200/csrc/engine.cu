@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "attn.cuh"
+#include "attn_cluster.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
 #include "gguf.h"
@@ -125,6 +126,7 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   const size_t budget = GEMV_SMEM_BUDGET;
   if (ring_off + 2 * (size_t)p.slot_bytes > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
   const int nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / p.slot_bytes);
+  p.early_stages = std::max(1, std::min(nstages, (int)(80 * 1024 / p.slot_bytes)));
   p.error_flag = e->d_error;
   const size_t smem = ring_off + (size_t)nstages * p.slot_bytes;
   const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
@@ -150,9 +152,63 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 }
 
 
+// B200_ATTN_CLUSTER=1 runs the engine's attention as one thread-block cluster per head
+// (attn_cluster.cuh) instead of the ticket kernel; measured slower inside the step graph so far.
+static bool attn_use_cluster() {
+  static const bool on = [] { const char* v = getenv("B200_ATTN_CLUSTER"); return v && atoi(v) != 0; }();
+  return on;
+}
+
+// Context splits per (sequence, head): about four CTAs per SM for the ticket kernel; for the
+// cluster kernel a power of two up to 8 (the portable cluster size), about two CTAs per SM.
 static int attn_nsplit(const b200_engine* e, int batch) {
-  int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
-  return std::max(1, std::min(want, 32));
+  if (!attn_use_cluster()) {
+    int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
+    return std::max(1, std::min(want, 32));
+  }
+  const int want = 2 * e->num_sms / std::max(1, e->nq * batch);
+  int cl = 1;
+  while (cl * 2 <= want && cl * 2 <= ATTC_MAX_CLUSTER) cl *= 2;
+  return cl;
+}
+
+// Starts decode attention: the cluster kernel when the split count is 1, 2, 4 or 8 (and the
+// ticket kernel is not forced), else the ticket kernel.
+static void launch_attention(const AttnParams& a, int batch, bool kv_i8, bool use_pdl, bool force_ticket, cudaStream_t st) {
+  const int ns = a.nsplit;
+  const bool cluster = !force_ticket && (ns == 1 || ns == 2 || ns == 4 || ns == 8);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(ns, a.nq, batch);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = ns;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+    cfg.blockDim = dim3(ATTC_THREADS);
+    cfg.dynamicSmemBytes = attc_smem_floats(a.hd) * sizeof(float);
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true>, a));
+    else CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false>, a));
+    return;
+  }
+  const size_t smem = attn_smem_bytes(a.hd, a.max_ctx, ns, 4);
+  if (smem > 160 * 1024) throw std::runtime_error("context too long for the requested split count");
+  cfg.blockDim = dim3(ATTN_GROUP_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, a));
+  else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a));
 }
 
 // Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
@@ -198,19 +254,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
       a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
       a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
-      const size_t smem = attn_smem_bytes(e->hd, e->max_ctx, nsplit, 4);
-      cudaLaunchConfig_t cfg{};
-      cfg.gridDim = dim3(nsplit, e->nq, batch);
-      cfg.blockDim = dim3(ATTN_GROUP_THREADS);
-      cfg.dynamicSmemBytes = smem;
-      cfg.stream = st;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = e->use_pdl ? 1 : 0;
-      if (e->desc.kv_dtype == B200_KV_I8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, a));
-      else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a));
+      launch_attention(a, batch, e->desc.kv_dtype == B200_KV_I8, e->use_pdl, !attn_use_cluster(), st);
       ++launches;
     }
     {

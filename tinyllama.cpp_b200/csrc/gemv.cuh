@@ -143,6 +143,7 @@ struct GemvParams {
   int K;                // input dimension, a multiple of 256
   int nblk, nslab, S, S_last, R;  // GemvGeom of K
   uint32_t slot_bytes;  // ring slot = the largest stage of the launch
+  int early_stages;     // stages the producer may request before the consumers hold the input vector
   const float* x;       // [batch][x_stride]
   int x_stride;
   const float* norm_w;  // RMSNorm weight fused into the prologue, or nullptr
@@ -206,11 +207,10 @@ __device__ __forceinline__ void consumer_sync();
 // extraction after a bias: v + 0x80...80 has bytes digit + 128, and xor 0x80 turns them into the
 // signed digits.
 
-// Quantises the eight elements v[] this lane holds of 256-element block b (after the optional
-// RMSNorm scaling) and writes the block's digit planes, digit sums and scale.
+// Quantises the eight elements v[] this lane holds of 256-element block b, whose largest
+// magnitude over the warp is amax, and writes the block's digit planes, digit sums and scale.
 template <int P>
-__device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int lane, const float (&vin)[8],
-                                                   const float* __restrict__ norm_w, const float4 (&nw)[2], float f) {
+__device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int lane, const float (&v)[8], float amax) {
   uint8_t* planes = const_cast<uint8_t*>(a.planes);
   float* sx = const_cast<float*>(a.sx);
   uint8_t* xs32d = const_cast<uint8_t*>(a.xs32d);
@@ -219,20 +219,8 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
   constexpr int QMAX = P == 3 ? 8355711 : (P == 2 ? 32639 : 127);
   constexpr int BIAS = P == 3 ? 0x808080 : (P == 2 ? 0x8080 : 0x80);
   const int e0 = b * 256 + lane * 8;
-  float v[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = vin[i];
-  if (norm_w) {
-    const float w[8] = {nw[0].x, nw[0].y, nw[0].z, nw[0].w, nw[1].x, nw[1].y, nw[1].z, nw[1].w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = v[i] * f * w[i];
-  }
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = warp_max(amax);
-  const float scale = amax / (float)QMAX;
-  const float inv = amax > 0.f ? (float)QMAX / amax : 0.f;
+  const float scale = amax * (1.0f / (float)QMAX);
+  const float inv = amax > 0.f ? __fdividef((float)QMAX, amax) : 0.f;  // any consistent inverse works: q is clamped to +-QMAX
   int s8 = 0;
   uint32_t u[8];
 #pragma unroll
@@ -267,15 +255,34 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
 // Prologue run by the 16 consumer warps: optional RMSNorm (reference utils.cpp:648-673: mean of
 // squares, f = 1/sqrtf(mean + eps), out = x*f*w) then quantisation into the image above. Each
 // warp owns the 256-element blocks warp, warp+16, ...; the vector is read from global memory once
-// (up to four blocks per warp stay in registers between the two passes).
-// XFN(i) returns element i of the input vector.
+// (up to four blocks per warp stay in registers between the two passes). The norm weights do not
+// depend on the previous kernel: they are requested first, and only then (dep_wait) does the
+// kernel wait for the grid it depends on, so their trip to HBM overlaps that wait.
+// XFN(e, v) loads elements e .. e+7 of the input vector.
+__device__ __forceinline__ void pdl_wait();
+__device__ __forceinline__ uint32_t smem_u32(const void* p);
+
+template <int P>
+__device__ __forceinline__ void act_scale_block(float (&v)[8], const float* __restrict__ norm_w, const float4 (&nw)[2], float f,
+                                                float& amax) {
+  if (norm_w) {
+    const float w[8] = {nw[0].x, nw[0].y, nw[0].z, nw[0].w, nw[1].x, nw[1].y, nw[1].z, nw[1].w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * f * w[i];
+  }
+  amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+}
+
 template <int P, typename XFN>
-__device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm_w, float eps, int K, float* red /* 18 floats */) {
+__device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm_w, float eps, int K, float* red /* 18 floats */,
+                          bool dep_wait, unsigned long long* gate) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nblk = K / 256;
   constexpr int KEEP = 4;
   float xv[KEEP][8];
-  float4 wv[KEEP][2];  // norm weights, requested together with x so the two latencies overlap
+  float4 wv[KEEP][2];
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < KEEP; ++k) {
@@ -285,6 +292,7 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
       wv[k][1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
     }
   }
+  if (dep_wait) pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
 #pragma unroll
   for (int k = 0; k < KEEP; ++k) {
     const int b = warp + k * GEMV_WARPS;
@@ -300,13 +308,19 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss = fmaf(t[i], t[i], ss);
   }
+  if (gate && lane == 0) {
+    // arrive only once the loads above have returned: the address is made to depend on their data
+    uint32_t z;
+    asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(gate) + z) : "memory");
+  }
   float f = 1.0f;
   if (norm_w) {
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
     consumer_sync();
-    // fixed-order pairwise sum of the 16 warp partials (the reference accumulates in double; FP64
-    // on this part costs more than a microsecond here and the difference is below 1e-7 relative)
+    // fixed-order pairwise sum of the 16 warp partials (the reference accumulates in double; the
+    // difference is below 1e-7 relative and FP64 is slow on this part)
     float r[GEMV_WARPS];
 #pragma unroll
     for (int w = 0; w < GEMV_WARPS; ++w) r[w] = red[w];
@@ -314,13 +328,25 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
     for (int n = GEMV_WARPS / 2; n > 0; n >>= 1)
 #pragma unroll
       for (int w = 0; w < n; ++w) r[w] = r[2 * w] + r[2 * w + 1];
-    f = 1.0f / sqrtf(r[0] / (float)K + eps);
+    f = rsqrtf(r[0] * (1.0f / (float)K) + eps);  // 2 ulp; the exact form costs a few hundred cycles of dependent latency here
   }
   const ActImage a = act_carve(smem, K, P);
+  // the blocks a warp holds go through the absmax reduction together, so their shuffle chains overlap
+  float amax[KEEP];
+#pragma unroll
+  for (int k = 0; k < KEEP; ++k) {
+    amax[k] = 0.f;
+    if (warp + k * GEMV_WARPS < nblk) act_scale_block<P>(xv[k], norm_w, wv[k], f, amax[k]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+      if (warp + k * GEMV_WARPS < nblk) amax[k] = fmaxf(amax[k], __shfl_xor_sync(0xffffffffu, amax[k], o));
 #pragma unroll
   for (int k = 0; k < KEEP; ++k) {
     const int b = warp + k * GEMV_WARPS;
-    if (b < nblk) act_quantize_block<P>(a, b, lane, xv[k], norm_w, wv[k], f);
+    if (b < nblk) act_quantize_block<P>(a, b, lane, xv[k], amax[k]);
   }
   for (int b = warp + KEEP * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {
     float t[8];
@@ -330,7 +356,9 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
       w2[0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
       w2[1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
     }
-    act_quantize_block<P>(a, b, lane, t, norm_w, w2, f);
+    float am;
+    act_scale_block<P>(t, norm_w, w2, f, am);
+    act_quantize_block<P>(a, b, lane, t, warp_max(am));
   }
   consumer_sync();
 }
@@ -555,6 +583,7 @@ __device__ __forceinline__ void gemv_locate(const GemvParams& p, int tile, int& 
 struct GemvShared {
   unsigned long long full_bar[GEMV_MAX_STAGES];
   unsigned long long empty_bar[GEMV_MAX_STAGES];
+  unsigned long long gate_bar;  // completes when every consumer warp holds its part of the input vector
   float red[GEMV_WARPS + 2];
   float part[GEMV_NTB][GEMV_WARPS][16];
   float sv[GEMV_WARPS];
@@ -580,6 +609,7 @@ __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
       mbar_init(&sh->full_bar[s], 1);
       mbar_init(&sh->empty_bar[s], GEMV_WARPS);
     }
+    mbar_init(&sh->gate_bar, GEMV_WARPS);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -595,6 +625,7 @@ __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh)
 // round-robin over the CTAs so that launches mixing formats of different cost stay balanced.
 __device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int cta, int ncta) {
   GemvShared* sh = pc.sh;
+  int issued = 0;
   for (int tile = cta; tile < prm.ntiles; tile += ncta) {
     int s, tl;
     gemv_locate(prm, tile, s, tl);
@@ -602,6 +633,10 @@ __device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc,
     const uint8_t* src = sg.img + (size_t)tl * sg.tile_bytes;
     for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
       const int slot = pc.slot, use = pc.use;
+      // The first stages are requested while the kernel still waits for its input, so that they
+      // land during that wait. The rest is held back until the consumers have read the input
+      // vector: its loads would otherwise queue behind a full ring of weight traffic on this SM.
+      if (issued++ == prm.early_stages && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->gate_bar, 0)) pipe_fail(prm, sh);
       if (use > 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
       const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
       mbar_expect_tx(&sh->full_bar[slot], bytes);
@@ -679,7 +714,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
                                              int& best_i) {
   GemvShared* sh = pc.sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red);
+  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, true, &sh->gate_bar);
   const ActImage a = act_carve(pc.act, prm.K, P);
 
   LaneCtx L;
@@ -799,7 +834,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
     if (threadIdx.x == GEMV_WARPS * 32) gemv_produce(prm, pc, blockIdx.x, gridDim.x);
     return;
   }
-  pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
