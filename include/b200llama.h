@@ -145,6 +145,14 @@ int b200_engine_stats(const b200_engine* e, int64_t* kernel_launches_per_step, i
  * distinct layers' weights and returns its mean CUDA-event duration and algorithmic bytes. */
 int b200_engine_time_kernel(b200_engine* e, int which, int iters, float* mean_us, int64_t* bytes_per_launch);
 
+/* Step trace (no counterpart in the reference, which has no timers besides total wall time, api.cpp:825-831).
+ * An engine created while B200_TRACE=1 is set in the environment gives every matvec and attention launch
+ * of a step a record of four device timestamps (GPU global timer, ns), written by the first thread of the
+ * launch's first CTA: kernel entry, inputs loaded, prologue done, that CTA's end. This call waits for the
+ * engine's stream and returns the records of the most recent step in launch order ([n][4]; launches that do
+ * not stamp, e.g. the embedding gather, stay zero). */
+int b200_engine_read_trace(b200_engine* e, uint64_t* out, int max_records, int* n_records);
+
 /* ---- tensor parallelism inside one node (no counterpart in the reference, whose MPI coordinator,
  * distributed_coordinator.cpp, only routes whole requests). One engine per GPU/process with
  * tp_rank/tp_size set and the same nccl_id; every rank uploads the WHOLE tensors (or loads the same

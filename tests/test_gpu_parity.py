@@ -68,6 +68,21 @@ def test_matvec_vs_kahan_dot(pkg, name, rows, cols, planes):
         assert float((np.abs(y - ref) / den).max()) <= 1e-3
 
 
+@pytest.mark.parametrize("name,rows,cols", [("q4_k", 7144, 4096), ("q6_k", 4800, 11008), ("q8_0", 7000, 2048),
+                                            ("q6_k", 9000, 4096), ("q4_k", 40300, 4096)])
+def test_matvec_many_tiles_per_cta(pkg, name, rows, cols):
+    """Shapes where every CTA walks several tiles: the ring of stages wraps, slots are refilled by the
+    last warp to leave them, and (last case) the parked partial sums are flushed more than once."""
+    typ = TYPES[name]
+    w = pkg.synth.fill_normal(rows * cols, 91, rows + typ, 0.02)
+    blocks = pkg.synth.quantize(typ, w)
+    x = pkg.synth.fill_normal(cols, 92, cols, 1.0)
+    wd = ol.dequant("oracle", typ, blocks).reshape(rows, cols)
+    ref = ol.matvec_f32("oracle", wd, x)
+    y = pkg.api.matvec(typ, blocks, rows, cols, x)
+    assert rel_err(y, ref) <= 1e-3
+
+
 def test_matvec_batch_and_edge_values(pkg):
     rows, cols = 8, 512
     w = pkg.synth.fill_normal(rows * cols, 5, 9, 0.02)
@@ -266,3 +281,24 @@ def test_upload_tensor_path_and_validation(pkg, tiny_models):
     assert np.array_equal(a, b)
     eng.close()
     ref.close()
+
+
+def test_step_trace_records(pkg, tiny_models, monkeypatch):
+    """B200_TRACE=1: every matvec / attention launch of a step leaves four ordered device timestamps."""
+    monkeypatch.setenv("B200_TRACE", "1")
+    eng = pkg.Engine.from_gguf(tiny_models[1])
+    monkeypatch.delenv("B200_TRACE")
+    eng.decode([3], [0])
+    eng.decode([5], [1])
+    t = eng.read_trace().astype(np.int64)
+    L = eng.desc.num_hidden_layers
+    assert len(t) == 3 + 5 * L
+    body = t[1:1 + 5 * L]
+    assert (body > 0).all()
+    assert (np.diff(body, axis=1) >= 0).all()          # entry <= inputs <= prologue <= end within a launch
+    assert (np.diff(body[:, 0]) > 0).all()             # launches enter in stream order
+    plain = pkg.Engine.from_gguf(tiny_models[1])
+    with pytest.raises(RuntimeError):
+        plain.read_trace()
+    plain.close()
+    eng.close()

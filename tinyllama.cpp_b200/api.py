@@ -30,7 +30,8 @@ EXPORTS = [
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
     "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_rmsnorm", "b200_attention_decode",
-    "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_nccl_unique_id", "b200_tp_share"]
+    "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
+    "b200_nccl_unique_id", "b200_tp_share"]
 
 _lib = None
 _vp, _i, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
@@ -66,6 +67,7 @@ def lib():
     L.b200_attention_decode_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
     L.b200_engine_stats.argtypes = [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.b200_engine_time_kernel.argtypes = [_vp, _i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i64)]
+    L.b200_engine_read_trace.argtypes = [_vp, _vp, _i, ctypes.POINTER(_i)]
     L.b200_nccl_unique_id.argtypes = [_vp]
     L.b200_tp_share.argtypes = [_i64, _i, _i, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     _lib = L
@@ -188,6 +190,13 @@ class Engine:
         a, b, c = _i64(0), _i64(0), _i64(0)
         _check(lib().b200_engine_stats(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)))
         return dict(launches_per_step=a.value, weight_bytes=b.value, kv_bytes_per_position=c.value)
+
+    def read_trace(self, max_records=4096):
+        """Device timestamps (ns) of the last step's launches, [n][4]; needs B200_TRACE=1 at engine creation."""
+        out = np.zeros((max_records, 4), np.uint64)
+        n = _i(0)
+        _check(lib().b200_engine_read_trace(self._h, out.ctypes.data_as(_vp), max_records, ctypes.byref(n)))
+        return out[:n.value].copy()
 
     def time_kernel(self, which, iters):
         us, nbytes = ctypes.c_float(0), _i64(0)

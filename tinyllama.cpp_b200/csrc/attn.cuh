@@ -38,6 +38,7 @@ struct AttnParams {
   float* out;            // [batch][out_stride]
   int out_stride;
   float att_scale;
+  unsigned long long* trace;  // optional step-trace record: entry, inputs ready, this CTA's partials written, end
 };
 
 constexpr int ATTN_GROUP_THREADS = 128;
@@ -296,11 +297,15 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
   // lets a dependent launch that opted in start its independent prologue (weight prefetch) now;
   // it still waits for this grid to finish before touching anything produced here
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
+  trace_stamp(rec, 0);
   // when launched as a programmatic dependent itself: q and the new K/V rows belong to the previous kernel until here
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  trace_stamp(rec, 1);
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   attn_item<KV_I8>(prm, split, h, b, sm, threadIdx.x, 1);
   __syncthreads();  // every thread's partials are written; one thread publishes them for the whole CTA
+  trace_stamp(rec, 2);
   if (threadIdx.x == 0) {
     __threadfence();
     const int old = atomicAdd(&prm.tickets[b * prm.nq + h], 1);
@@ -308,9 +313,13 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
     if (last_flag) __threadfence();
   }
   __syncthreads();
-  if (!last_flag) return;
+  if (!last_flag) {
+    trace_stamp(rec, 3);
+    return;
+  }
   attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd, sm, 1);
   if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
+  trace_stamp(rec, 3);
 }
 
 inline size_t attn_smem_bytes(int hd, int max_ctx, int nsplit, int /*nwarps*/) {

@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
   extern __shared__ __align__(16) float sm[];
   cg::cluster_group cluster = cg::this_cluster();
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
+  trace_stamp(rec, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
   const int hd = prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
@@ -43,6 +45,7 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
 
   // q and the new K/V rows belong to the previous kernel until here
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  trace_stamp(rec, 1);
   const int pos = prm.positions[b], slot = prm.slots[b];
   const int T = pos + 1;
   constexpr int EPL = KV_I8 ? 16 : 4;  // elements per lane per row (one 16-byte load)
@@ -215,6 +218,7 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
       cres[hd + 1] = Lc;
     }
   }
+  trace_stamp(rec, 2);
   cluster.sync();
   // ---- the CTAs of the cluster, in split order, by the first one ----
   if (cluster.block_rank() == 0) {
@@ -248,6 +252,7 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
       dst[d] = o * inv;
     }
   }
+  trace_stamp(rec, 3);
   cluster.sync();  // remote shared memory stays alive until the first CTA has read it
 }
 

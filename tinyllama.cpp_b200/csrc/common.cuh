@@ -9,6 +9,17 @@
 
 namespace b200 {
 
+// Step trace: when a launch is given a record (four 64-bit slots), the first thread of its first
+// CTA writes the GPU's global nanosecond timer there at fixed points of the kernel.
+__device__ __forceinline__ void trace_stamp(unsigned long long* rec, int col) {
+  if (rec) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    rec[col] = t;
+  }
+}
+
+
 enum : int { T_F32 = 0, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14 };
 
 struct CudaError : std::runtime_error {

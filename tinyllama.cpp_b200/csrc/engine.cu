@@ -211,6 +211,11 @@ static void launch_attention(const AttnParams& a, int batch, bool kv_i8, bool us
   else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a));
 }
 
+// Step-trace record of the launch with this index within the step (nullptr when tracing is off).
+static unsigned long long* trace_rec(const b200_engine* e, int launch_index) {
+  return e->d_trace && launch_index < e->trace_cap ? e->d_trace + 4 * (size_t)launch_index : nullptr;
+}
+
 // Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
 static int tp_reduce_add(b200_engine* e, int batch, cudaStream_t st) {
   Nccl& n = Nccl::get();
@@ -243,6 +248,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
       p.y = e->d_q; p.y_stride = e->Hq; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
       p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
+      p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
     }
@@ -254,6 +260,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
       a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
       a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      a.trace = trace_rec(e, launches);
       launch_attention(a, batch, e->desc.kv_dtype == B200_KV_I8, e->use_pdl, !attn_use_cluster(), st);
       ++launches;
     }
@@ -261,6 +268,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->d_attn; p.x_stride = e->Hq; p.epi = tp ? EPI_STORE : EPI_RESID;
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
+      p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
       if (tp) launches += tp_reduce_add(e, batch, st);
@@ -270,6 +278,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.seg[0] = seg_of(w.wgu); p.nseg = 1;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
       p.y = e->d_act; p.y_stride = F;
+      p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
     }
@@ -277,6 +286,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = tp ? EPI_STORE : EPI_RESID;
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
+      p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
       if (tp) launches += tp_reduce_add(e, batch, st);
@@ -291,6 +301,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
     p.amax_val = tp ? e->d_amax_val + half : e->d_amax_val; p.amax_idx = tp ? e->d_amax_idx + half : e->d_amax_idx;
     p.amax_row_offset = e->tp_rank * e->Vl;
+    p.trace = trace_rec(e, launches);
     const int grid = launch_gemv(e, p, batch, st);
     ++launches;
     if (tp) {

@@ -53,6 +53,9 @@ struct b200_engine {
   int num_sms = 148;
   bool use_pdl = true;
   int* d_error = nullptr;
+  unsigned long long* d_trace = nullptr;  // B200_TRACE=1: one 4-slot timestamp record per launch of a step
+  int trace_cap = 0;
+  int last_launches = 0;
   bool finalized = false;
   cudaStream_t stream = nullptr;
   std::vector<b200::LayerW> layers;

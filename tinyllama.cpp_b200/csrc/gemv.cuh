@@ -16,11 +16,12 @@
 // Data movement. Weights live in HBM as "stage images": the matrix is cut into tiles of 16*R
 // rows and slabs of S <= 16 blocks along K, and each (tile, slab) is stored as one contiguous
 // run laid out exactly as it will sit in shared memory (rows padded to a stride = 32 mod 128 so
-// the fragment loads are free of bank conflicts). One persistent CTA per SM walks its tiles; a
-// single producer thread moves every stage with ONE bulk asynchronous copy (cp.async.bulk,
-// completion counted on an mbarrier) into a ring of shared-memory slots, so HBM sees runs of
-// 20-70 KB and several stages are in flight without holding registers. The 16 consumer warps
-// each take one (row group, block) task of the staged slab. When a row has at most 16 blocks a
+// the fragment loads are free of bank conflicts). One persistent CTA per SM walks its tiles;
+// every stage moves with ONE bulk asynchronous copy (cp.async.bulk, completion counted on an
+// mbarrier) into a ring of shared-memory slots, so HBM sees runs of 20-70 KB and several stages
+// are in flight without holding registers. There is no producer warp: the warp that is last to
+// finish with a slot requests the stage that goes into it next, so all 512 threads compute and
+// each may use 128 registers. The 16 warps each take one (row group, block) task of the staged slab. When a row has at most 16 blocks a
 // warp meets the same block column in every tile, and its B fragments (the activation digits)
 // stay in registers for the whole launch. Partial row sums are parked in shared memory and the
 // rows of up to 16 tiles are finished together, in a fixed order (deterministic), by all threads.
@@ -36,8 +37,8 @@
 namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
-constexpr int GEMV_WARPS = 16;                        // consumer warps
-constexpr int GEMV_THREADS = (GEMV_WARPS + 1) * 32;   // + one producer warp
+constexpr int GEMV_WARPS = 16;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 8;
 constexpr int GEMV_NTB = 16;                          // tiles whose partial sums are parked before their rows are finished
 constexpr int GEMV_SMEM_BUDGET = 208 * 1024;          // dynamic shared memory (activation image + ring)
@@ -143,7 +144,7 @@ struct GemvParams {
   int K;                // input dimension, a multiple of 256
   int nblk, nslab, S, S_last, R;  // GemvGeom of K
   uint32_t slot_bytes;  // ring slot = the largest stage of the launch
-  int early_stages;     // stages the producer may request before the consumers hold the input vector
+  int early_stages;     // stages requested before the kernel holds its input vector (the rest of the ring right after)
   const float* x;       // [batch][x_stride]
   int x_stride;
   const float* norm_w;  // RMSNorm weight fused into the prologue, or nullptr
@@ -163,6 +164,7 @@ struct GemvParams {
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
+  unsigned long long* trace;  // optional step-trace record: entry, input vector loaded, prologue done, end
 };
 
 // ---- shared-memory activation image ------------------------------------------------------
@@ -258,7 +260,8 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
 // (up to four blocks per warp stay in registers between the two passes). The norm weights do not
 // depend on the previous kernel: they are requested first, and only then (dep_wait) does the
 // kernel wait for the grid it depends on, so their trip to HBM overlaps that wait.
-// XFN(e, v) loads elements e .. e+7 of the input vector.
+// XFN(e, v) loads elements e .. e+7 of the input vector; AFTERX(ss) is called by every thread
+// right after its part of the vector has been requested and summed.
 __device__ __forceinline__ void pdl_wait();
 __device__ __forceinline__ uint32_t smem_u32(const void* p);
 
@@ -275,9 +278,9 @@ __device__ __forceinline__ void act_scale_block(float (&v)[8], const float* __re
   for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 }
 
-template <int P, typename XFN>
+template <int P, typename XFN, typename AFTERX>
 __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm_w, float eps, int K, float* red /* 18 floats */,
-                          bool dep_wait, unsigned long long* gate) {
+                          bool dep_wait, AFTERX after_x) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nblk = K / 256;
   constexpr int KEEP = 4;
@@ -308,12 +311,7 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss = fmaf(t[i], t[i], ss);
   }
-  if (gate && lane == 0) {
-    // arrive only once the loads above have returned: the address is made to depend on their data
-    uint32_t z;
-    asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(gate) + z) : "memory");
-  }
+  after_x(ss);  // runs once the loads above have returned (it is handed a value computed from them)
   float f = 1.0f;
   if (norm_w) {
     ss = warp_sum(ss);
@@ -582,8 +580,7 @@ __device__ __forceinline__ void gemv_locate(const GemvParams& p, int tile, int& 
 // ---- the streaming pipeline ----------------------------------------------------------------
 struct GemvShared {
   unsigned long long full_bar[GEMV_MAX_STAGES];
-  unsigned long long empty_bar[GEMV_MAX_STAGES];
-  unsigned long long gate_bar;  // completes when every consumer warp holds its part of the input vector
+  int arrivals[GEMV_MAX_STAGES];  // warps that have finished with the stage in each slot
   float red[GEMV_WARPS + 2];
   float part[GEMV_NTB][GEMV_WARPS][16];
   float sv[GEMV_WARPS];
@@ -596,8 +593,9 @@ struct PipeCtx {
   uint8_t* act;   // activation image
   uint8_t* ring;  // nstages slots of slot_bytes
   int nstages;
-  int slot;       // ring slot of the next stage (producer and consumers count alike)
+  int slot;       // ring slot of the stage the warps work on next
   int use;        // how many times the ring has wrapped
+  int ptile, pslab;  // the stage that will be requested next (same value in every thread)
   __device__ __forceinline__ void next_stage() {
     if (++slot == nstages) { slot = 0; ++use; }
   }
@@ -607,9 +605,8 @@ __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < nstages; ++s) {
       mbar_init(&sh->full_bar[s], 1);
-      mbar_init(&sh->empty_bar[s], GEMV_WARPS);
+      sh->arrivals[s] = 0;
     }
-    mbar_init(&sh->gate_bar, GEMV_WARPS);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -621,28 +618,21 @@ __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh)
   if (prm.error_flag) atomicExch(prm.error_flag, 1);
 }
 
-// The producer (one thread): one bulk copy per stage of this CTA's tiles. Tiles are dealt
-// round-robin over the CTAs so that launches mixing formats of different cost stay balanced.
-__device__ __forceinline__ void gemv_produce(const GemvParams& prm, PipeCtx& pc, int cta, int ncta) {
-  GemvShared* sh = pc.sh;
-  int issued = 0;
-  for (int tile = cta; tile < prm.ntiles; tile += ncta) {
-    int s, tl;
-    gemv_locate(prm, tile, s, tl);
-    const GemvSeg& sg = prm.seg[s];
-    const uint8_t* src = sg.img + (size_t)tl * sg.tile_bytes;
-    for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
-      const int slot = pc.slot, use = pc.use;
-      // The first stages are requested while the kernel still waits for its input, so that they
-      // land during that wait. The rest is held back until the consumers have read the input
-      // vector: its loads would otherwise queue behind a full ring of weight traffic on this SM.
-      if (issued++ == prm.early_stages && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->gate_bar, 0)) pipe_fail(prm, sh);
-      if (use > 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->empty_bar[slot], (use - 1) & 1)) pipe_fail(prm, sh);
-      const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
-      mbar_expect_tx(&sh->full_bar[slot], bytes);
-      bulk_g2s(pc.ring + (size_t)slot * prm.slot_bytes, src + (size_t)slab * sg.stage_bytes, bytes, &sh->full_bar[slot]);
-    }
-  }
+// Requests stage (tile, slab) into ring slot `slot` with one bulk copy (called by one thread).
+__device__ __forceinline__ void gemv_request(const GemvParams& prm, const PipeCtx& pc, int slot, int tile, int slab) {
+  int s, tl;
+  gemv_locate(prm, tile, s, tl);
+  const GemvSeg& sg = prm.seg[s];
+  const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
+  mbar_expect_tx(&pc.sh->full_bar[slot], bytes);
+  bulk_g2s(pc.ring + (size_t)slot * prm.slot_bytes, sg.img + (size_t)tl * sg.tile_bytes + (size_t)slab * sg.stage_bytes, bytes,
+           &pc.sh->full_bar[slot]);
+}
+
+// Advances the request cursor by one stage. Tiles are dealt round-robin over the CTAs so that
+// launches mixing formats of different cost stay balanced.
+__device__ __forceinline__ void gemv_cursor_next(const GemvParams& prm, PipeCtx& pc, int ncta) {
+  if (++pc.pslab == prm.nslab) { pc.pslab = 0; pc.ptile += ncta; }
 }
 
 // Finishes the rows of the n tiles parked in sh->part (tiles first_i .. first_i+n-1 of this CTA's
@@ -714,7 +704,27 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
                                              int& best_i) {
   GemvShared* sh = pc.sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, true, &sh->gate_bar);
+  // The first early_stages stages were requested at kernel start, so that they land while the
+  // kernel still waits for its input. The rest of the ring is requested as soon as this thread's
+  // part of the input vector has arrived: behind a full ring of weight traffic on this SM those
+  // loads would wait for microseconds.
+  const int early = prm.early_stages;
+  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
+  auto after_x = [&](float ss) {
+    if (threadIdx.x == 0) {
+      uint32_t z;
+      asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));  // issue order: after the loads have returned
+      trace_stamp(rec, 1);
+      int pt = pc.ptile, ps = pc.pslab;
+      for (int k = (int)z; k < pc.nstages && pt < prm.ntiles; ++k) {
+        if (k >= early) gemv_request(prm, pc, k, pt, ps);
+        if (++ps == prm.nslab) { ps = 0; pt += ncta; }
+      }
+    }
+  };
+  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, true, after_x);
+  trace_stamp(rec, 2);
+  for (int k = 0; k < pc.nstages; ++k) gemv_cursor_next(prm, pc, ncta);  // the cursor now points past the initial fill
   const ActImage a = act_carve(pc.act, prm.K, P);
 
   LaneCtx L;
@@ -764,7 +774,12 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->empty_bar[slot]);
+      // the last warp to finish with this slot requests the stage that goes into it next
+      if (lane == 0 && atomicAdd(&sh->arrivals[slot], 1) == GEMV_WARPS - 1) {
+        sh->arrivals[slot] = 0;  // ordered before the other warps' next visit by the request's barrier arrive
+        if (pc.ptile < prm.ntiles) gemv_request(prm, pc, slot, pc.ptile, pc.pslab);
+      }
+      gemv_cursor_next(prm, pc, ncta);
     }
     // ---- tile finished: fold the four k-slices and park the partial sums ----
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
@@ -826,19 +841,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
   pc.nstages = nstages;
   pc.slot = 0;
   pc.use = 0;
+  pc.ptile = blockIdx.x;
+  pc.pslab = 0;
   pipe_init(&sh, nstages);
   pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5;
-  if (warp >= GEMV_WARPS) {
-    // weights never depend on the previous kernel, so the producer starts before the consumers' dependency wait
-    if (threadIdx.x == GEMV_WARPS * 32) gemv_produce(prm, pc, blockIdx.x, gridDim.x);
-    return;
+  // weights never depend on the previous kernel: the first stages are requested before the dependency wait
+  if (threadIdx.x == 0) {
+    int pt = pc.ptile, ps = 0;
+    for (int k = 0; k < nstages && k < prm.early_stages && pt < prm.ntiles; ++k) {
+      gemv_request(prm, pc, k, pt, ps);
+      if (++ps == prm.nslab) { ps = 0; pt += gridDim.x; }
+    }
   }
+  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
+  trace_stamp(rec, 0);
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
   gemv_consume<P, BREG>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
   if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
+  trace_stamp(rec, 3);
 }
 
 }  // namespace b200
