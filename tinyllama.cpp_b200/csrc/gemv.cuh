@@ -256,8 +256,7 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
 
 // Prologue run by the 16 consumer warps: optional RMSNorm (reference utils.cpp:648-673: mean of
 // squares, f = 1/sqrtf(mean + eps), out = x*f*w) then quantisation into the image above. Each
-// warp owns the 256-element blocks warp, warp+16, ...; the vector is read from global memory once
-// (up to four blocks per warp stay in registers between the two passes). The norm weights do not
+// warp owns the 256-element blocks warp, warp+16, .... The norm weights do not
 // depend on the previous kernel: they are requested first, and only then (dep_wait) does the
 // kernel wait for the grid it depends on, so their trip to HBM overlaps that wait.
 // XFN(e, v) loads elements e .. e+7 of the input vector; AFTERX(ss) is called by every thread
@@ -283,29 +282,35 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
                           bool dep_wait, AFTERX after_x) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nblk = K / 256;
-  constexpr int KEEP = 4;
-  float xv[KEEP][8];
-  float4 wv[KEEP][2];
-  float ss = 0.f;
-#pragma unroll
-  for (int k = 0; k < KEEP; ++k) {
-    const int b = warp + k * GEMV_WARPS;
-    if (b < nblk && norm_w) {
-      wv[k][0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
-      wv[k][1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
-    }
+  // This code runs once per launch, from a cold instruction cache, so it is kept small. The warp's
+  // first three blocks stay in registers between the two passes; further blocks (rows longer than
+  // 12288) are read again.
+  float xv[8];
+  float4 wv[2];
+  wv[0] = wv[1] = make_float4(1.f, 1.f, 1.f, 1.f);
+  if (warp < nblk && norm_w) {
+    wv[0] = __ldg(reinterpret_cast<const float4*>(norm_w + warp * 256 + lane * 8));
+    wv[1] = __ldg(reinterpret_cast<const float4*>(norm_w + warp * 256 + lane * 8 + 4));
   }
   if (dep_wait) pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
+  float ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < KEEP; ++k) {
-    const int b = warp + k * GEMV_WARPS;
-    if (b < nblk) {
-      xfn(b * 256 + lane * 8, xv[k]);
+  for (int i = 0; i < 8; ++i) xv[i] = 0.f;
+  if (warp < nblk) {
+    xfn(warp * 256 + lane * 8, xv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(xv[k][i], xv[k][i], ss);
-    }
+    for (int i = 0; i < 8; ++i) ss = fmaf(xv[i], xv[i], ss);
   }
-  for (int b = warp + KEEP * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {  // very long vectors: extra blocks are re-read later
+  // the warp's second and third block (rows of up to 12288 elements) are requested now as well and kept
+  float x1[8], x2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x1[i] = x2[i] = 0.f;
+  if (warp + GEMV_WARPS < nblk) xfn((warp + GEMV_WARPS) * 256 + lane * 8, x1);
+  if (warp + 2 * GEMV_WARPS < nblk) xfn((warp + 2 * GEMV_WARPS) * 256 + lane * 8, x2);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = fmaf(x2[i], x2[i], fmaf(x1[i], x1[i], ss));
+#pragma unroll 1
+  for (int b = warp + 3 * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {
     float t[8];
     xfn(b * 256 + lane * 8, t);
 #pragma unroll
@@ -329,34 +334,40 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
     f = rsqrtf(r[0] * (1.0f / (float)K) + eps);  // 2 ulp; the exact form costs a few hundred cycles of dependent latency here
   }
   const ActImage a = act_carve(smem, K, P);
-  // the blocks a warp holds go through the absmax reduction together, so their shuffle chains overlap
-  float amax[KEEP];
-#pragma unroll
-  for (int k = 0; k < KEEP; ++k) {
-    amax[k] = 0.f;
-    if (warp + k * GEMV_WARPS < nblk) act_scale_block<P>(xv[k], norm_w, wv[k], f, amax[k]);
+  {
+    float amax;
+    act_scale_block<P>(xv, norm_w, wv, f, amax);
+    if (warp < nblk) act_quantize_block<P>(a, warp, lane, xv, warp_max(amax));
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-    for (int k = 0; k < KEEP; ++k)
-      if (warp + k * GEMV_WARPS < nblk) amax[k] = fmaxf(amax[k], __shfl_xor_sync(0xffffffffu, amax[k], o));
-#pragma unroll
-  for (int k = 0; k < KEEP; ++k) {
-    const int b = warp + k * GEMV_WARPS;
-    if (b < nblk) act_quantize_block<P>(a, b, lane, xv[k], amax[k]);
-  }
-  for (int b = warp + KEEP * GEMV_WARPS; b < nblk; b += GEMV_WARPS) {
-    float t[8];
-    xfn(b * 256 + lane * 8, t);
-    float4 w2[2];
-    if (norm_w) {
-      w2[0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
-      w2[1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
+  // rows longer than 4096: the remaining blocks two at a time, so that their shuffle chains overlap
+#pragma unroll 1
+  for (int b = warp + GEMV_WARPS; b < nblk; b += 2 * GEMV_WARPS) {
+    const int b2 = b + GEMV_WARPS;
+    const bool two = b2 < nblk;
+    float4 w1[2], w2[2];
+    w1[0] = w1[1] = w2[0] = w2[1] = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (b != warp + GEMV_WARPS) {  // beyond the blocks kept in registers: read again
+      xfn(b * 256 + lane * 8, x1);
+      if (two) xfn(b2 * 256 + lane * 8, x2);
     }
-    float am;
-    act_scale_block<P>(t, norm_w, w2, f, am);
-    act_quantize_block<P>(a, b, lane, t, warp_max(am));
+    if (norm_w) {
+      w1[0] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8));
+      w1[1] = __ldg(reinterpret_cast<const float4*>(norm_w + b * 256 + lane * 8 + 4));
+      if (two) {
+        w2[0] = __ldg(reinterpret_cast<const float4*>(norm_w + b2 * 256 + lane * 8));
+        w2[1] = __ldg(reinterpret_cast<const float4*>(norm_w + b2 * 256 + lane * 8 + 4));
+      }
+    }
+    float a1, a2 = 0.f;
+    act_scale_block<P>(x1, norm_w, w1, f, a1);
+    if (two) act_scale_block<P>(x2, norm_w, w2, f, a2);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, o));
+      a2 = fmaxf(a2, __shfl_xor_sync(0xffffffffu, a2, o));
+    }
+    act_quantize_block<P>(a, b, lane, x1, a1);
+    if (two) act_quantize_block<P>(a, b2, lane, x2, a2);
   }
   consumer_sync();
 }
