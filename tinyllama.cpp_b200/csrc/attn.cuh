@@ -72,15 +72,19 @@ __device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, in
   }
   group_sync(bar_id);
   float M = -INFINITY;
+#pragma unroll 1
   for (int s = 0; s < prm.nsplit; ++s) M = fmaxf(M, m_s[s]);
   if (gtid < prm.nsplit) w_s[gtid] = l_s[gtid] > 0.f ? expf(m_s[gtid] - M) : 0.f;
   group_sync(bar_id);
   float L = 0.f;
+#pragma unroll 1
   for (int s = 0; s < prm.nsplit; ++s)
     if (l_s[s] > 0.f) L += l_s[s] * w_s[s];
   const float inv = 1.0f / (L + 1e-9f);
+#pragma unroll 1
   for (int d = gtid; d < prm.hd; d += nthr) {
     float o = 0.f;
+#pragma unroll 1
     for (int s0 = 0; s0 < prm.nsplit; s0 += 16) {  // sixteen loads in flight at a time
       float v[16];
 #pragma unroll
@@ -94,12 +98,14 @@ __device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, in
 }
 
 // One (split, head, sequence) item by a group of 128 threads. KV_I8: int8 rows, 16 elements per
-// lane per row; else FP32 rows, 4 elements per lane. sm = this group's shared memory.
-template <bool KV_I8>
+// lane per row; else FP32 rows, 4 elements per lane. sm = this group's shared memory. HD: the head
+// dimension when known at compile time (the lane-to-position mapping then folds to constants and
+// the code shrinks, which matters: the kernel runs from a cold instruction cache), 0 = read prm.hd.
+template <bool KV_I8, int HD>
 __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float* sm, int gtid, int bar_id) {
   const int lane = gtid & 31, warp = gtid >> 5;
   constexpr int nwarps = ATTN_GROUP_THREADS / 32;
-  const int hd = prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
+  const int hd = HD ? HD : prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
   const int pos = prm.positions[b], slot = prm.slots[b];
   const int T = pos + 1;
   int chunk = (T + prm.nsplit - 1) / prm.nsplit;
@@ -122,10 +128,12 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
     float* dst_s = warp == 0 ? kn_s : vn_s;
     if (KV_I8) {
       float amax = 0.f;
+#pragma unroll 1
       for (int d = lane; d < hd; d += 32) amax = fmaxf(amax, fabsf(src[d]));
       amax = warp_max(amax);
       const float scale = ((double)amax > 1e-8) ? __fdiv_rn(amax, 127.0f) : 1.0f;
       int8_t* crow = reinterpret_cast<int8_t*>(warp == 0 ? prm.k_cache : prm.v_cache) + (head_row0 + pos) * hd;
+#pragma unroll 1
       for (int d = lane; d < hd; d += 32) {
         float r = roundf(__fdiv_rn(src[d], scale));
         r = fmaxf(-127.0f, fminf(127.0f, r));
@@ -136,6 +144,7 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
       if (h % G == 0 && lane == 0) (warp == 0 ? prm.k_scale : prm.v_scale)[head_row0 + pos] = scale;
     } else {
       float* crow = reinterpret_cast<float*>(warp == 0 ? prm.k_cache : prm.v_cache) + (head_row0 + pos) * hd;
+#pragma unroll 1
       for (int d = lane; d < hd; d += 32) {
         const float v = src[d];
         dst_s[d] = v;
@@ -174,6 +183,7 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
   }
 
   // ---- scores: U rows per lane requested before any is used ----
+#pragma unroll 1
   for (int tb = t0 + warp * ppw * U; tb < t1; tb += nwarps * ppw * U) {
     uint4 kw[U];
     float ks[U];
@@ -212,12 +222,14 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
   // ---- max and exp-sum over this split ----
   const int n = max(t1 - t0, 0);
   float m = -INFINITY;
+#pragma unroll 1
   for (int i = gtid; i < n; i += ATTN_GROUP_THREADS) m = fmaxf(m, sc_s[i]);
   m = warp_max(m);
   if (lane == 0) red[warp] = m;
   group_sync(bar_id);
   m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   float l = 0.f;
+#pragma unroll 1
   for (int i = gtid; i < n; i += ATTN_GROUP_THREADS) {
     const float p = expf(sc_s[i] - m);
     sc_s[i] = p;
@@ -232,6 +244,7 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
   float acc[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
+#pragma unroll 1
   for (int tb = t0 + warp * ppw * U; tb < t1; tb += nwarps * ppw * U) {
     uint4 vw[U];
     float ps[U];
@@ -290,7 +303,7 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
 }
 
 // Stand-alone kernel: one group per CTA, ticket merge by the last CTA of each (sequence, head).
-template <bool KV_I8>
+template <bool KV_I8, int HD>
 __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(const AttnParams prm) {
   extern __shared__ __align__(16) float sm[];
   __shared__ int last_flag;
@@ -303,7 +316,7 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
   asm volatile("griddepcontrol.wait;" ::: "memory");
   trace_stamp(rec, 1);
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  attn_item<KV_I8>(prm, split, h, b, sm, threadIdx.x, 1);
+  attn_item<KV_I8, HD>(prm, split, h, b, sm, threadIdx.x, 1);
   __syncthreads();  // every thread's partials are written; one thread publishes them for the whole CTA
   trace_stamp(rec, 2);
   if (threadIdx.x == 0) {

@@ -26,7 +26,7 @@ constexpr int ATTC_MAX_CLUSTER = 8;
 // floats of dynamic shared memory: q, new K row, new V row, per-warp (o[hd], m, l), CTA (o[hd], m, l)
 __host__ __device__ __forceinline__ size_t attc_smem_floats(int hd) { return (size_t)3 * hd + (size_t)(ATTC_WARPS + 1) * (hd + 2); }
 
-template <bool KV_I8>
+template <bool KV_I8, int HD>
 __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const AttnParams prm) {
   namespace cg = cooperative_groups;
   extern __shared__ __align__(16) float sm[];
@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
   trace_stamp(rec, 0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, nsplit = gridDim.x, h = blockIdx.y, b = blockIdx.z;
-  const int hd = prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
+  const int hd = HD ? HD : prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
   float* q_s = sm;
   float* kn_s = q_s + hd;
   float* vn_s = kn_s + hd;

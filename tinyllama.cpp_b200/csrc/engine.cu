@@ -30,12 +30,14 @@ static void set_gemv_attrs() {
   static bool done = false;
   if (done) return;
   const int maxb = GEMV_SMEM_BUDGET;
-  CK(cudaFuncSetAttribute((gemv_kernel<2, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((gemv_kernel<2, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((gemv_kernel<3, false>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute((gemv_kernel<3, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-  CK(cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<true, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<false, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<true, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_decode_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   done = true;
 }
 
@@ -140,14 +142,8 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = e->use_pdl ? 1 : 0;
-  const bool breg = p.nslab == 1;
-  if (e->P == 2) {
-    if (breg) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2, true>, p, nstages));
-    else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2, false>, p, nstages));
-  } else {
-    if (breg) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3, true>, p, nstages));
-    else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3, false>, p, nstages));
-  }
+  if (e->P == 2) CK(cudaLaunchKernelEx(&cfg, gemv_kernel<2>, p, nstages));
+  else CK(cudaLaunchKernelEx(&cfg, gemv_kernel<3>, p, nstages));
   return gx;
 }
 
@@ -197,8 +193,16 @@ static void launch_attention(const AttnParams& a, int batch, bool kv_i8, bool us
     cfg.dynamicSmemBytes = attc_smem_floats(a.hd) * sizeof(float);
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true>, a));
-    else CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false>, a));
+    if (a.hd == 128) {
+      if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true, 128>, a));
+      else CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false, 128>, a));
+    } else if (a.hd == 64) {
+      if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true, 64>, a));
+      else CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false, 64>, a));
+    } else {
+      if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true, 0>, a));
+      else CK(cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false, 0>, a));
+    }
     return;
   }
   const size_t smem = attn_smem_bytes(a.hd, a.max_ctx, ns, 4);
@@ -207,8 +211,16 @@ static void launch_attention(const AttnParams& a, int batch, bool kv_i8, bool us
   cfg.dynamicSmemBytes = smem;
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, a));
-  else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a));
+  if (a.hd == 128) {
+    if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true, 128>, a));
+    else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false, 128>, a));
+  } else if (a.hd == 64) {
+    if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true, 64>, a));
+    else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false, 64>, a));
+  } else {
+    if (kv_i8) CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true, 0>, a));
+    else CK(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false, 0>, a));
+  }
 }
 
 // Step-trace record of the launch with this index within the step (nullptr when tracing is off).

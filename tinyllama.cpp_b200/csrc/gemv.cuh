@@ -654,6 +654,7 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
   const int tid = threadIdx.x, lane = tid & 31;
   const int R = prm.R, S = prm.S;
   const int total = n * R * 16;
+#pragma unroll 1
   for (int base = (tid & ~31); base < total; base += GEMV_WARPS * 32) {
     const int idx = base + lane;
     const bool in = idx < total;
@@ -663,6 +664,7 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
     float tot = 0.f;
     if (in) {
       const float* pp = &sh->part[slot][rgi * S][r];
+#pragma unroll 4
       for (int s = 0; s < S; ++s) tot += pp[s * 16];
     }
     int seg, tl;
@@ -710,7 +712,7 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
 
 // The 16 consumer warps: prologue, then one (row group, block) task per warp per stage; the rows
 // are finished GEMV_NTB tiles at a time.
-template <int P, bool BREG, typename XFN>
+template <int P, typename XFN>
 __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc, XFN xfn, int bidx, int cta, int ncta, float& best_v,
                                              int& best_i) {
   GemvShared* sh = pc.sh;
@@ -747,8 +749,12 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
   const bool rg_ok = rg < prm.R;
   BFrag bf;
   int cur_type = -1;
+  // rows of at most 16 blocks: one stage per tile, the warp meets the same block column every
+  // time and its B fragments stay in registers until the block type changes
+  const bool breg = prm.nslab == 1;
 
   int i = 0;
+#pragma unroll 1
   for (int tile = cta; tile < prm.ntiles; tile += ncta, ++i) {
     int s, tl;
     gemv_locate(prm, tile, s, tl);
@@ -756,13 +762,14 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
     const int type = sg.type;
     const int ub = gemv_unit_bytes(type);
     float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll 1
     for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
       const int slot = pc.slot, use = pc.use;
       const bool last = slab == prm.nslab - 1;
       const bool active = rg_ok && bi < (last ? prm.S_last : prm.S);
       // the activation digits are ready before the weights: fetch them ahead of the wait (with at
       // most 16 blocks per row the warp meets the same block every time and keeps them)
-      if (active && (!BREG || type != cur_type)) {
+      if (active && (!breg || type != cur_type)) {
         load_bfrag<P>(type, a, slab * prm.S + bi, L, bf);
         cur_type = type;
       }
@@ -802,9 +809,9 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
       sh->part[pp][warp][L.g] = acc0;
       sh->part[pp][warp][L.g + 8] = acc1;
     }
-    if (pp == GEMV_NTB - 1) gemv_flush(prm, sh, i - pp, GEMV_NTB, bidx, cta, ncta, best_v, best_i);
+    // rows are finished when GEMV_NTB tiles are parked or after the CTA's last tile (one call site: code size)
+    if (pp == GEMV_NTB - 1 || tile + ncta >= prm.ntiles) gemv_flush(prm, sh, i - pp, pp + 1, bidx, cta, ncta, best_v, best_i);
   }
-  if (i % GEMV_NTB) gemv_flush(prm, sh, i - i % GEMV_NTB, i % GEMV_NTB, bidx, cta, ncta, best_v, best_i);
 }
 
 // Per-CTA (value, first index) of the rows this CTA produced, from the per-thread running bests.
@@ -840,8 +847,9 @@ struct XFromGlobal {
 };
 
 // One launch = one fused matvec for blockIdx.y's activation vector; one persistent CTA per SM.
-// BREG: rows have at most 16 blocks (one stage per tile), so B fragments stay in registers.
-template <int P, bool BREG>
+// There is one instantiation per activation width only: a decode step alternates between this
+// kernel and the attention kernel 160 times, and their code should stay in the instruction cache.
+template <int P>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm, int nstages) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ GemvShared sh;
@@ -869,7 +877,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
-  gemv_consume<P, BREG>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
+  gemv_consume<P>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
   if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
   trace_stamp(rec, 3);
 }

@@ -39,9 +39,11 @@ __global__ void select_kernel(const SelectParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int step = *p.step_counter;
   const int fsteps = p.forced ? *p.forced_steps : 0;
+#pragma unroll 1
   for (int b = warp; b < p.batch; b += nwarps) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
+#pragma unroll 1
     for (int i = lane; i < p.nparts; i += 32) {
       const size_t at = ((size_t)(i / p.parts_per_rank) * p.batch + b) * p.parts_per_rank + (i % p.parts_per_rank);
       const float v = p.amax_val[at];
