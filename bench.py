@@ -251,7 +251,9 @@ def main():
             "data": "synthetic",
             "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len, "kv_cache": kv,
                        "context_during_timing": [prompt_len + warmup, prompt_len + warmup + args.steps],
-                       "parallelism": "single GPU" if world == 1 else f"tp{world} (column-split QKV/gate/up/head, row-split O/down, NCCL all-reduce)",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world} (column-split QKV/gate/up/head, row-split O/down, " +
+                                      ("one-shot all-reduce over peer memory inside the matvec kernels" if st["launches_per_step"] == 3 + 5 * L
+                                       else "NCCL all-reduce") + ", NCCL all-gather of logits)",
                        "l2": "weights read per step (GBs) exceed the 126 MB L2; no flush needed",
                        "act_planes": args.planes, "load_s": round(t_load, 2), "prefill_s": round(t_prefill, 2)},
             "e2e": {"value": e2e_tps, "unit": "tokens/s", "h2d_bytes_per_step": 12 * batch,

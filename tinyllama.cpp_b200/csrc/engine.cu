@@ -247,6 +247,38 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   const int H = e->H, F = e->F, KVD = e->KVD;
   const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
   const bool tp = e->tp_size > 1;
+  // Tensor parallelism over peer memory (e->use_peer): the O and down projections store their
+  // partial rows into every rank's exchange slots (exchange k of the step uses slot set k & 1),
+  // and the next matvec adds the tp slots to the residual stream in its prologue and stores the
+  // new stream to the other of two buffers. There are 2L exchanges per step, so the stream is back
+  // in d_h when the step ends.
+  const bool peer = tp && e->use_peer;
+  const size_t slots_bytes = (size_t)2 * e->tp_size * e->max_seqs * H * sizeof(float);
+  auto slot_of = [&](void* region, int k, int src) {
+    return static_cast<float*>(region) + ((size_t)(k & 1) * e->tp_size + src) * e->max_seqs * H;
+  };
+  auto flag_of = [&](void* region, int k, int src) {
+    return reinterpret_cast<unsigned*>(static_cast<uint8_t*>(region) + slots_bytes) + (k & 1) * e->tp_size + src;
+  };
+  float* hcur = e->d_h;
+  float* hnext = e->d_h2;
+  int pending = -1;  // exchange whose sum the next matvec has to pick up
+  auto as_producer = [&](GemvParams& p, int k) {
+    p.epi = EPI_PEER; p.tp = e->tp_size; p.tp_rank = e->tp_rank; p.y = nullptr; p.y_stride = H;
+    for (int r = 0; r < e->tp_size; ++r) { p.peer_y[r] = slot_of(e->peer_region[r], k, e->tp_rank); p.peer_flag[r] = flag_of(e->peer_region[r], k, e->tp_rank); }
+    p.peer_ticket = e->d_peer_ticket; p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)k + 1u;
+    pending = k;
+  };
+  auto as_consumer = [&](GemvParams& p) {
+    p.x = hcur;
+    if (pending < 0) return;
+    p.tp = e->tp_size; p.tp_rank = e->tp_rank;
+    p.x_parts = slot_of(e->xregion, pending, 0); p.parts_stride = (size_t)e->max_seqs * H;
+    p.wait_flags = flag_of(e->xregion, pending, 0); p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)pending + 1u;
+    p.x_out = hnext;
+    std::swap(hcur, hnext);
+    pending = -1;
+  };
   if (with_embed) {
     embed_kernel<<<batch, 256, 0, st>>>(e->d_tokens, e->tok_embd.f32(), e->d_h, H, e->V);
     CK(cudaGetLastError());
@@ -258,6 +290,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wq); p.seg[1] = seg_of(w.wk); p.seg[2] = seg_of(w.wv); p.nseg = 3;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
+      if (peer) as_consumer(p);
       p.y = e->d_q; p.y_stride = e->Hq; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
       p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
       p.trace = trace_rec(e, launches);
@@ -280,15 +313,17 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->d_attn; p.x_stride = e->Hq; p.epi = tp ? EPI_STORE : EPI_RESID;
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
+      if (peer) as_producer(p, 2 * l);
       p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
-      if (tp) launches += tp_reduce_add(e, batch, st);
+      if (tp && !peer) launches += tp_reduce_add(e, batch, st);
     }
     {
       GemvParams p{};
       p.seg[0] = seg_of(w.wgu); p.nseg = 1;
       p.K = H; p.x = e->d_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
+      if (peer) as_consumer(p);
       p.y = e->d_act; p.y_stride = F;
       p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
@@ -298,16 +333,18 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       GemvParams p{};
       p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->d_act; p.x_stride = F; p.epi = tp ? EPI_STORE : EPI_RESID;
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
+      if (peer) as_producer(p, 2 * l + 1);
       p.trace = trace_rec(e, launches);
       launch_gemv(e, p, batch, st);
       ++launches;
-      if (tp) launches += tp_reduce_add(e, batch, st);
+      if (tp && !peer) launches += tp_reduce_add(e, batch, st);
     }
   }
   {
     GemvParams p{};
     p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->d_h; p.x_stride = H;
     p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE;
+    if (peer) as_consumer(p);
     // each rank computes its share of the vocabulary; shares and argmax partials are then gathered
     const size_t half = (size_t)e->max_seqs * e->amax_cap * e->tp_size;
     p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
@@ -328,6 +365,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid * e->tp_size; s.parts_per_rank = grid; s.batch = batch;
     s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
     s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
+    if (peer) { s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L; }
     select_kernel<<<1, 256, 0, st>>>(s);
     CK(cudaGetLastError());
     ++launches;

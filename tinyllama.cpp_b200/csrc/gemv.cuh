@@ -36,7 +36,8 @@
 
 namespace b200 {
 
-enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
+enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_PEER = 4 };
+constexpr int GEMV_MAX_TP = 8;
 constexpr int GEMV_WARPS = 16;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 8;
@@ -165,6 +166,23 @@ struct GemvParams {
   int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
   unsigned long long* trace;  // optional step-trace record: entry, input vector loaded, prologue done, end
+  // ---- tensor-parallel exchange without a collective call (one-shot all-reduce over peer memory) ----
+  // Producer side (EPI_PEER): the partial output rows are stored into the exchange buffer of every
+  // rank (peer_y[r]: [batch][y_stride] slot of this rank in rank r's memory); the last CTA to finish
+  // then publishes the exchange number in every rank's flag word (peer_flag[r]).
+  // Consumer side (x_parts != nullptr): the input vector is x + the tp slots of the local exchange
+  // buffer, summed in rank order; the kernel first waits (bounded) until every rank's flag has
+  // reached this exchange's number, and its first CTA stores the sum to x_out.
+  int tp, tp_rank;
+  float* peer_y[GEMV_MAX_TP];
+  unsigned* peer_flag[GEMV_MAX_TP];
+  unsigned* peer_ticket;        // CTAs of this launch that have stored their rows (returns to 0)
+  const unsigned* epoch_base;   // device scalar: exchanges completed before this step
+  unsigned epoch_k;             // 1 + index of this launch's exchange within the step
+  const float* x_parts;         // [tp][parts_stride] local exchange slots to add to x
+  size_t parts_stride;
+  const unsigned* wait_flags;   // [tp] local flag words of that exchange buffer
+  float* x_out;                 // [batch][x_stride] where CTA 0 stores the summed input
 };
 
 // ---- shared-memory activation image ------------------------------------------------------
@@ -257,7 +275,7 @@ __device__ __forceinline__ void act_quantize_block(const ActImage& a, int b, int
 // Prologue run by the 16 consumer warps: optional RMSNorm (reference utils.cpp:648-673: mean of
 // squares, f = 1/sqrtf(mean + eps), out = x*f*w) then quantisation into the image above. Each
 // warp owns the 256-element blocks warp, warp+16, .... The norm weights do not
-// depend on the previous kernel: they are requested first, and only then (dep_wait) does the
+// depend on the previous kernel: they are requested first, and only then (before_x) does the
 // kernel wait for the grid it depends on, so their trip to HBM overlaps that wait.
 // XFN(e, v) loads elements e .. e+7 of the input vector; AFTERX(ss) is called by every thread
 // right after its part of the vector has been requested and summed.
@@ -277,9 +295,9 @@ __device__ __forceinline__ void act_scale_block(float (&v)[8], const float* __re
   for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 }
 
-template <int P, typename XFN, typename AFTERX>
+template <int P, typename XFN, typename BEFOREX, typename AFTERX>
 __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm_w, float eps, int K, float* red /* 18 floats */,
-                          bool dep_wait, AFTERX after_x) {
+                          BEFOREX before_x, AFTERX after_x) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nblk = K / 256;
   // This code runs once per launch, from a cold instruction cache, so it is kept small. The warp's
@@ -292,7 +310,7 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
     wv[0] = __ldg(reinterpret_cast<const float4*>(norm_w + warp * 256 + lane * 8));
     wv[1] = __ldg(reinterpret_cast<const float4*>(norm_w + warp * 256 + lane * 8 + 4));
   }
-  if (dep_wait) pdl_wait();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
+  before_x();  // the activation vector (and the buffers this kernel writes) belong to the previous kernel until here
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) xv[i] = 0.f;
@@ -626,7 +644,7 @@ __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
 
 __device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh) {
   sh->abort_flag = 1;
-  if (prm.error_flag) atomicExch(prm.error_flag, 1);
+  if (prm.error_flag) *reinterpret_cast<volatile int*>(prm.error_flag) = 1;  // host-mapped word: a plain store
 }
 
 // Requests stage (tile, slab) into ring slot `slot` with one bulk copy (called by one thread).
@@ -682,7 +700,9 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
       const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
       if (valid) {
         const int row = irow;
-        if (prm.epi == EPI_RESID) {
+        if (prm.epi == EPI_PEER) {
+          for (int r = 0; r < prm.tp; ++r) prm.peer_y[r][(size_t)bidx * prm.y_stride + row] = tot;
+        } else if (prm.epi == EPI_RESID) {
           const float* rs = (prm.resid ? prm.resid : prm.y) + (size_t)bidx * prm.y_stride + row;
           prm.y[(size_t)bidx * prm.y_stride + row] = *rs + tot;
         } else if (prm.epi == EPI_QKV_ROPE) {
@@ -735,7 +755,26 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
       }
     }
   };
-  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, true, after_x);
+  auto before_x = [&]() {
+    pdl_wait();
+    if (prm.wait_flags) {  // tensor parallel: the other ranks' partial sums must have landed in this GPU's memory
+      if ((int)threadIdx.x < prm.tp && (int)threadIdx.x != prm.tp_rank) {
+        const unsigned want = *prm.epoch_base + prm.epoch_k;
+        const volatile unsigned* f = prm.wait_flags + threadIdx.x;
+        int it = 0;
+        while ((int)(*f - want) < 0) {
+          if (++it > (1 << 24)) {  // bounded (seconds): report instead of hanging when a rank has gone away
+            pipe_fail(prm, sh);
+            break;
+          }
+          __nanosleep(100);
+        }
+        __threadfence_system();
+      }
+      consumer_sync();
+    }
+  };
+  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, before_x, after_x);
   trace_stamp(rec, 2);
   for (int k = 0; k < pc.nstages; ++k) gemv_cursor_next(prm, pc, ncta);  // the cursor now points past the initial fill
   const ActImage a = act_carve(pc.act, prm.K, P);
@@ -838,11 +877,29 @@ __device__ __forceinline__ void gemv_store_argmax(const GemvParams& prm, GemvSha
 
 __host__ __device__ __forceinline__ size_t gemv_ring_offset(int K, int P) { return (act_smem_bytes(K, P) + 127) / 128 * 128; }
 
-struct XFromGlobal {
+// Loads eight elements of the input vector; under tensor parallelism adds the ranks' partial sums
+// (in rank order, so every rank computes the same bits) and lets the first CTA store the total.
+struct XLoad {
   const float* x;
+  const float* parts;  // nullptr: plain load
+  size_t parts_stride;
+  int nparts;
+  float* out;          // nullptr: do not store
   __device__ __forceinline__ void operator()(int e, float (&v)[8]) const {
     const float4 a = *reinterpret_cast<const float4*>(x + e), b = *reinterpret_cast<const float4*>(x + e + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    if (parts) {
+#pragma unroll 1
+      for (int r = 0; r < nparts; ++r) {  // written by other GPUs: read past L1
+        const float4 c = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)r * parts_stride + e));
+        const float4 d = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)r * parts_stride + e + 4));
+        v[0] += c.x; v[1] += c.y; v[2] += c.z; v[3] += c.w; v[4] += d.x; v[5] += d.y; v[6] += d.z; v[7] += d.w;
+      }
+      if (out) {
+        *reinterpret_cast<float4*>(out + e) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(out + e + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    }
   }
 };
 
@@ -876,9 +933,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
   trace_stamp(rec, 0);
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
-  XFromGlobal xfn{prm.x + (size_t)blockIdx.y * prm.x_stride};
+  XLoad xfn{prm.x + (size_t)blockIdx.y * prm.x_stride, prm.x_parts ? prm.x_parts + (size_t)blockIdx.y * prm.x_stride : nullptr,
+            prm.parts_stride, prm.tp, (prm.x_out && blockIdx.x == 0) ? prm.x_out + (size_t)blockIdx.y * prm.x_stride : nullptr};
   gemv_consume<P>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
   if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
+  if (prm.epi == EPI_PEER && threadIdx.x == 0) {
+    // every thread's stores were issued before the barrier that ends the last flush; make them
+    // visible system-wide, and let the last CTA of the launch publish the exchange number
+    __threadfence_system();
+    if (atomicAdd(prm.peer_ticket, 1u) == gridDim.x * gridDim.y - 1) {
+      atomicExch(prm.peer_ticket, 0u);
+      __threadfence_system();
+      const unsigned ep = *prm.epoch_base + prm.epoch_k;
+      for (int r = 0; r < prm.tp; ++r)
+        if (r != prm.tp_rank) *reinterpret_cast<volatile unsigned*>(prm.peer_flag[r]) = ep;
+    }
+  }
   trace_stamp(rec, 3);
 }
 

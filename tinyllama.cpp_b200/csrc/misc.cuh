@@ -33,6 +33,8 @@ struct SelectParams {
   const int* forced_steps;// device scalar
   int* log;               // [log_cap][batch]
   int log_cap;
+  unsigned* epoch;        // tensor-parallel exchange counter to advance at the end of the step, or nullptr
+  unsigned epoch_inc;
 };
 
 __global__ void select_kernel(const SelectParams p) {
@@ -66,7 +68,10 @@ __global__ void select_kernel(const SelectParams p) {
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) *p.step_counter = step + 1;
+  if (threadIdx.x == 0) {
+    *p.step_counter = step + 1;
+    if (p.epoch) *p.epoch += p.epoch_inc;
+  }
 }
 
 // h[i] += partial[i]: the residual add after a tensor-parallel all-reduce.

@@ -28,7 +28,7 @@ struct Nccl {
   int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   void* handle = nullptr;
-  static constexpr int kFloat32 = 7, kInt32 = 2, kSum = 0;  // ncclFloat32, ncclInt32, ncclSum
+  static constexpr int kFloat32 = 7, kInt32 = 2, kInt8 = 0, kSum = 0, kMin = 3;  // ncclFloat32, ncclInt32, ncclInt8; ncclSum, ncclMin
 
   static Nccl& get() {
     static Nccl n;
