@@ -230,7 +230,7 @@ def main():
     # algorithmic bytes by the mean ratio of the others. Other workloads: no capture, null.
     traffic = None
     if args.workload == "c3-llama2-7b-q4km-bs1" and world == 1:
-        ncu_mb = {"gate_up_swiglu": 52.047, "qkv_rope": 38.336, "down_proj": 33.959, "o_proj": 10.758}
+        ncu_mb = {"gate_up_swiglu": 51.530, "qkv_rope": 32.998, "down_proj": 38.268, "o_proj": 9.667}
         ratio = sum(ncu_mb.values()) * 1e6 / sum(kern[k]["bytes"] for k in ncu_mb)
         tot = sum(ncu_mb[k] * 1e6 * kinds[k][1] for k in ncu_mb) + ratio * kern["lm_head"]["bytes"]
         traffic = int(tot / gemv_launches)
