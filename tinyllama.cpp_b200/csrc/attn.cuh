@@ -54,17 +54,24 @@ __host__ __device__ __forceinline__ size_t attn_group_floats(int hd, int max_ctx
 }
 
 constexpr int ATTN_MAX_SPLITS = 64;
+constexpr int ATTN_MERGE_AHEAD = 32;  // partial outputs requested before the (max, sum) pairs are known
 
-// Merges the per-split partials of (sequence b, head h) in split order. All loads of a phase are
-// issued together (one L2 round trip for the (max, sum) pairs, one for the partial outputs)
-// instead of one dependent load per split. scratch: 3 * ATTN_MAX_SPLITS floats of shared memory;
-// called by all nthr threads of the group, which synchronise on bar_id.
+// Merges the per-split partials of (sequence b, head h) in split order. Everything the merge reads
+// is requested in one go: the partial outputs of up to 32 splits go into registers while the
+// (max, sum) pairs make their own trip, so the whole merge costs one L2 round trip instead of one
+// per split. scratch: 3 * ATTN_MAX_SPLITS floats of shared memory; called by all nthr threads of
+// the group, which synchronise on bar_id.
 __device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, int h, int gtid, int nthr, float* dst, float* scratch,
                                                 int bar_id) {
   const size_t pbase = ((size_t)b * prm.nq + h) * prm.nsplit;
   float* m_s = scratch;
   float* l_s = scratch + ATTN_MAX_SPLITS;
   float* w_s = scratch + 2 * ATTN_MAX_SPLITS;
+  float v[ATTN_MERGE_AHEAD];
+  const int d0 = gtid;  // first output element of this thread
+#pragma unroll
+  for (int s = 0; s < ATTN_MERGE_AHEAD; ++s)
+    v[s] = (s < prm.nsplit && d0 < prm.hd) ? __ldcg(&prm.part_o[(pbase + s) * prm.hd + d0]) : 0.f;
   if (gtid < prm.nsplit) {
     const float2 ml = __ldcg(reinterpret_cast<const float2*>(&prm.part_ml[(pbase + gtid) * 2]));
     m_s[gtid] = ml.x;
@@ -82,17 +89,18 @@ __device__ __forceinline__ void attn_merge_head(const AttnParams& prm, int b, in
     if (l_s[s] > 0.f) L += l_s[s] * w_s[s];
   const float inv = 1.0f / (L + 1e-9f);
 #pragma unroll 1
-  for (int d = gtid; d < prm.hd; d += nthr) {
+  for (int d = d0; d < prm.hd; d += nthr) {
     float o = 0.f;
+    if (d == d0) {
+#pragma unroll
+      for (int s = 0; s < ATTN_MERGE_AHEAD; ++s)
+        if (s < prm.nsplit) o = fmaf(w_s[s], v[s], o);
+    } else {
 #pragma unroll 1
-    for (int s0 = 0; s0 < prm.nsplit; s0 += 16) {  // sixteen loads in flight at a time
-      float v[16];
-#pragma unroll
-      for (int s = 0; s < 16; ++s) v[s] = s0 + s < prm.nsplit ? __ldcg(&prm.part_o[(pbase + s0 + s) * prm.hd + d]) : 0.f;
-#pragma unroll
-      for (int s = 0; s < 16; ++s)
-        if (s0 + s < prm.nsplit) o = fmaf(w_s[s0 + s], v[s], o);
+      for (int s = 0; s < prm.nsplit && s < ATTN_MERGE_AHEAD; ++s) o = fmaf(w_s[s], __ldcg(&prm.part_o[(pbase + s) * prm.hd + d]), o);
     }
+#pragma unroll 1
+    for (int s = ATTN_MERGE_AHEAD; s < prm.nsplit; ++s) o = fmaf(w_s[s], __ldcg(&prm.part_o[(pbase + s) * prm.hd + d]), o);
     dst[d] = o * inv;
   }
 }

@@ -159,7 +159,8 @@ static bool attn_use_cluster() {
 // cluster kernel a power of two up to 8 (the portable cluster size), about two CTAs per SM.
 static int attn_nsplit(const b200_engine* e, int batch) {
   if (!attn_use_cluster()) {
-    int want = (4 * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
+    static const int per_sm = [] { const char* v = getenv("B200_ATTN_CTAS_PER_SM"); return v && atoi(v) > 0 ? atoi(v) : 4; }();
+    int want = (per_sm * e->num_sms + e->nq * batch - 1) / (e->nq * batch);
     return std::max(1, std::min(want, 32));
   }
   const int want = 2 * e->num_sms / std::max(1, e->nq * batch);
