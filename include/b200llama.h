@@ -110,6 +110,12 @@ int b200_dequant(int ggml_type, const void* host_blocks, size_t n_blocks, float*
  * matvec_f32_f32_cuda (cuda_kernels.cu:291-314) / matvec_*_f32_vector_cpu (utils.cpp:293-397). */
 int b200_matvec(int ggml_type, const void* host_blocks, int64_t rows, int64_t cols, const float* host_x,
                 int batch, int act_planes, float* host_y);
+/* Y[t][r] = dot(W[r,:], X[t,:]) for n_tokens rows of X on the tensor cores (tcgen05, fp16 operands, FP32
+ * accumulation in tensor memory): the batch >= 16 / prompt path that replaces matmul_*_f32_batch_cpu
+ * (utils.cpp:730-782, 890-1044) and smart_gemm_batch_cuda (model.cpp:2141-2249). host_x [n_tokens][cols],
+ * host_y [n_tokens][rows]. Agrees with the FP32 dot to about 1e-3 of the largest output. */
+int b200_matmul(int ggml_type, const void* host_blocks, int64_t rows, int64_t cols, const float* host_x, int n_tokens,
+                float* host_y);
 /* rmsnorm_vector_cuda (cuda_kernels.cu:209-253, 2499) */
 int b200_rmsnorm(const float* host_x, const float* host_w, int n, float eps, float* host_out);
 /* Decode attention of one new token over a cache of n_ctx earlier positions (attention_cuda,

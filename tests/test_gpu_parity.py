@@ -83,6 +83,22 @@ def test_matvec_many_tiles_per_cta(pkg, name, rows, cols):
     assert rel_err(y, ref) <= 1e-3
 
 
+@pytest.mark.parametrize("name,rows,cols,tokens", [("q4_k", 128, 256, 16), ("q8_0", 64, 256, 16), ("q6_k", 130, 512, 32),
+                                                   ("q4_k", 1024, 4096, 64), ("q6_k", 512, 11008, 48), ("q4_k", 300, 1024, 300),
+                                                   ("q8_0", 520, 2048, 17)])
+def test_matmul_tensor_core(pkg, name, rows, cols, tokens):
+    """The tcgen05 / TMEM matmul (batch >= 16 and prompt path) against the FP64 product of the dequantised
+    weights. Operands are rounded to fp16, so the tolerance is 2e-3 of the largest output (measured 3e-4)."""
+    typ = TYPES[name]
+    w = pkg.synth.fill_normal(rows * cols, 11, rows + typ, 0.02)
+    blocks = pkg.synth.quantize(typ, w)
+    x = pkg.synth.fill_normal(tokens * cols, 12, cols, 1.0).reshape(tokens, cols)
+    wd = ol.dequant("oracle", typ, blocks).reshape(rows, cols)
+    ref = (wd.astype(np.float64) @ x.astype(np.float64).T).T
+    y = pkg.api.matmul(typ, blocks, rows, cols, x)
+    assert np.abs(y - ref).max() <= 2e-3 * np.abs(ref).max()
+
+
 def test_matvec_batch_and_edge_values(pkg):
     rows, cols = 8, 512
     w = pkg.synth.fill_normal(rows * cols, 5, 9, 0.02)

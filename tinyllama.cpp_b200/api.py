@@ -29,7 +29,7 @@ EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
-    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_rmsnorm", "b200_attention_decode",
+    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_attention_decode",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
     "b200_nccl_unique_id", "b200_tp_share"]
 
@@ -67,6 +67,7 @@ def lib():
     L.b200_attention_decode_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
     L.b200_engine_stats.argtypes = [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.b200_engine_time_kernel.argtypes = [_vp, _i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i64)]
+    L.b200_matmul.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _vp]
     L.b200_engine_read_trace.argtypes = [_vp, _vp, _i, ctypes.POINTER(_i)]
     L.b200_nccl_unique_id.argtypes = [_vp]
     L.b200_tp_share.argtypes = [_i64, _i, _i, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
@@ -217,6 +218,15 @@ def matvec(ggml_type, blocks, rows, cols, x, act_planes=3):
     y = np.empty((batch, rows), np.float32)
     _check(lib().b200_matvec(ggml_type, _ptr(blocks), rows, cols, _ptr(x), batch, act_planes, _ptr(y)))
     return y[0] if x.ndim == 1 else y
+
+
+def matmul(ggml_type, blocks, rows, cols, x):
+    """Tensor-core path: x [n_tokens][cols] -> y [n_tokens][rows]."""
+    blocks, x = np.ascontiguousarray(blocks, np.uint8), _f32(x)
+    assert x.ndim == 2 and x.shape[1] == cols
+    y = np.empty((x.shape[0], rows), np.float32)
+    _check(lib().b200_matmul(ggml_type, _ptr(blocks), rows, cols, _ptr(x), x.shape[0], _ptr(y)))
+    return y
 
 
 def rmsnorm(x, w, eps):

@@ -10,6 +10,7 @@
 #include "attn_cluster.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
+#include "gemm_tc.cuh"
 #include "gguf.h"
 #include "misc.cuh"
 #include "tp.h"
@@ -147,6 +148,29 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   return gx;
 }
 
+
+// Starts the tensor-core matmul for T tokens (gemm_tc.cuh). x16: [T][K] fp16 activations.
+static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
+    attr_done = true;
+  }
+  const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
+  p.nblk = g0.nblk; p.nslab = g0.nslab; p.S = g0.S; p.S_last = g0.S_last; p.R = g0.R;
+  // token tile: the whole batch when it fits one tile, else 256 / 128 (two accumulator tiles of 256 columns fit TMEM, one is used)
+  int NT = (p.T + 15) / 16 * 16;
+  if (NT > TC_MAX_N) NT = TC_MAX_N;
+  p.NT = NT;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < NT) p.tmem_cols *= 2;
+  p.ntiles_m = 0;
+  for (int s = 0; s < p.nseg; ++s) p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
+  p.error_flag = e->d_error;
+  dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT);
+  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
+  CK(cudaGetLastError());
+}
 
 // B200_ATTN_CLUSTER=1 runs the engine's attention as one thread-block cluster per head
 // (attn_cluster.cuh) instead of the ticket kernel; measured slower inside the step graph so far.

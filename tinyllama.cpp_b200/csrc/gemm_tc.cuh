@@ -1,0 +1,358 @@
+// Batched matmul on the 5th-generation tensor cores for batch >= 16 decode and prompt ingestion:
+//   Y[t][row] = sum_k W[row][k] * X[t][k]        (W packed Q8_0 / Q4_K / Q6_K, X fp16, fp32 accumulate)
+// Replaces matmul_*_f32_batch_cpu (reference utils.cpp:730-782, 890-1044) / smart_gemm_batch_cuda
+// (model.cpp:2141-2249). "Swap-AB": the weight rows are the M side of the MMA (128 per CTA tile),
+// the tokens the N side (16..256 per tile).
+//
+// Per 64-element step along K the CTA's 256 threads
+//   * read the packed units of their weight row straight from the stage images, dequantise 32
+//     elements each to fp16 and store them into the A tile (128 rows x 128 bytes) in the K-major
+//     128-byte-swizzle layout the MMA unit reads from shared memory;
+//   * copy the matching slice of the fp16 activations into the B tile (N rows x 128 bytes, same layout);
+// then one thread issues four tcgen05.mma (M=128, N, K=16, kind::f16) that accumulate into a
+// 128-lane x N-column fp32 tile in tensor memory and commits them to an mbarrier. Two A/B stages
+// alternate, so the dequantisation of step i+1 overlaps the MMAs of step i. After the last step
+// the warps read their TMEM lanes back (tcgen05.ld 32x32b: thread = weight row, registers =
+// tokens) and run the same epilogues as the matvec kernel (store, residual add, RoPE scatter,
+// SwiGLU). Every wait is bounded; on a give-up the kernel sets the error word, frees its tensor
+// memory and returns.
+//
+// fp16 operands: dequantised weights are rounded to fp16 (relative 2^-11) and activations likewise,
+// so results agree with the FP32 reference dot to about 1e-3 of the largest output, not to 1e-3 of
+// each element; the parity tests state that tolerance.
+#pragma once
+#include "gemv.cuh"
+
+namespace b200 {
+
+constexpr int TC_M = 128;        // weight rows per CTA tile (the MMA's M)
+constexpr int TC_KC = 64;        // elements along K per shared-memory stage: one 128-byte swizzled row of fp16
+constexpr int TC_THREADS = 256;
+constexpr int TC_MAX_N = 256;
+
+struct TcParams {
+  GemvSeg seg[3];
+  int nseg;
+  int K;
+  int nblk, nslab, S, S_last, R;  // GemvGeom of K (where a unit sits inside the stage images)
+  const __half* x16;              // [T][K] activations (already normalised when the layer asks for it)
+  int T;                          // tokens
+  int NT;                         // tokens per CTA tile: a multiple of 16, <= 256
+  int tmem_cols;                  // power of two >= max(32, NT)
+  int epi;                        // EPI_STORE / EPI_RESID / EPI_QKV_ROPE / EPI_SWIGLU
+  float* y;                       // [T][y_stride]
+  int y_stride;
+  float* y2;                      // QKV: new K then V rows, [T][y2_stride]
+  int y2_stride;
+  const float* resid;             // RESID: y = resid + W x (nullptr: y itself)
+  const float* rope;
+  const int* positions;           // [T]
+  int head_dim, max_pos;
+  int ntiles_m;                   // 128-row tiles over all segments
+  int* error_flag;
+};
+
+// ---- tcgen05 / TMEM primitives (inline PTX) ---------------------------------------------------
+__device__ __forceinline__ void tc_alloc(uint32_t* smem_dst, int ncols) {  // one full warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, int ncols) {  // the same warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 fp16 per instruction
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// arrives on the mbarrier once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void tc_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// this warp's 32 TMEM lanes, 8 consecutive columns: thread = lane, registers = columns
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte-swizzle layout: rows of 128
+// bytes, 8-row groups 1024 bytes apart, 16-byte chunk c of row r stored at chunk c ^ (r & 7).
+// Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (1: unused with this
+// swizzle), stride byte offset >> 4 [32,46) (1024 >> 4), descriptor version 1 [46,48), layout
+// type 2 = SWIZZLE_128B [61,64). A step of 16 elements along K advances the start by 32 bytes.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor, kind::f16: D = F32 [4,6) = 1, A and B = F16 (0) and K-major (0),
+// N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ __forceinline__ uint32_t tc_idesc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24); }
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// 16-byte chunk c (0..7) of row r in a swizzled tile
+__device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// Address of unit (image row, block) inside a segment's stage images, and of the row's Q6_K scale
+// array (see GemvGeom): the batched kernel reads the same images the matvec kernel streams.
+struct TcUnit {
+  const uint8_t* unit;
+  const uint8_t* d;  // Q6_K: this block's fp16 d
+};
+__device__ __forceinline__ TcUnit tc_locate(const TcParams& p, const GemvSeg& sg, int irow, int blk) {
+  const int tr = 16 * p.R;
+  const int tile = irow / tr, rr = irow - tile * tr;
+  const int slab = blk / p.S, bb = blk - slab * p.S;
+  const bool last = slab == p.nslab - 1;
+  const uint8_t* rowp = sg.img + (size_t)tile * sg.tile_bytes + (size_t)slab * sg.stage_bytes + (size_t)rr * (last ? sg.RS_last : sg.RS);
+  TcUnit u;
+  u.unit = rowp + (size_t)bb * gemv_unit_bytes(sg.type);
+  u.d = rowp + (last ? sg.d_off_last : sg.d_off) + 2 * bb;
+  return u;
+}
+
+// Dequantises 32 consecutive elements of a row: elements [64*kc + 32*half, +32) of 256-element
+// block `u`, to fp16, into four 16-byte chunks w[0..3] (eight halves each).
+// Formulas: reference dequantize_q4_k_m / dequantize_q6_k / dequantize_q8_0_block
+// (quantization.cpp:171-266, 1047-1052) with the products fused (the matmul contract is a tolerance).
+__device__ __forceinline__ void tc_dequant32(int type, const TcUnit& u, int kc, int half, uint4 (&w)[4]) {
+  float v[32];
+  if (type == T_Q4_K) {
+    const uint4 h = __ldg(reinterpret_cast<const uint4*>(u.unit));
+    const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+    const int sb = 2 * kc + half;  // 32-element sub-block
+    // get_scale_min_k4 (quantization.cpp:145-155) on the 12 scale bytes h.y h.z h.w
+    auto q = [&](int i) -> int {  // byte i of the 12 scale bytes
+      const uint32_t wv = i < 4 ? h.y : (i < 8 ? h.z : h.w);
+      return (int)((wv >> (8 * (i & 3))) & 0xFF);
+    };
+    int sc, mn;
+    if (sb < 4) {
+      sc = q(sb) & 63;
+      mn = q(sb + 4) & 63;
+    } else {
+      sc = (q(sb + 4) & 0xF) | ((q(sb - 4) >> 6) << 4);
+      mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
+    }
+    const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc + 16));
+    const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t byte = (qs[i >> 2] >> (8 * (i & 3))) & 0xFF;
+      const float qv = (float)(half ? (byte >> 4) : (byte & 15));
+      v[i] = fmaf(d1, qv, -m1);
+    }
+  } else if (type == T_Q6_K) {
+    const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
+    const float d = half_bits_to_float(__ldg(reinterpret_cast<const uint16_t*>(u.d)));
+    const uint8_t* ql = u.unit + 64 * hh + 32 * (j & 1);
+    const uint8_t* qh = u.unit + 128 + 32 * hh;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(u.unit + 192) + 8 * hh + 2 * j;
+    const uint4 la = __ldg(reinterpret_cast<const uint4*>(ql)), lb = __ldg(reinterpret_cast<const uint4*>(ql + 16));
+    const uint4 ha = __ldg(reinterpret_cast<const uint4*>(qh)), hb = __ldg(reinterpret_cast<const uint4*>(qh + 16));
+    const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+    const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+    const float s0 = d * (float)sc[0], s1 = d * (float)sc[1];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t lbyte = (lw[i >> 2] >> (8 * (i & 3))) & 0xFF, hbyte = (hw[i >> 2] >> (8 * (i & 3))) & 0xFF;
+      const int nib = (j >> 1) ? (int)(lbyte >> 4) : (int)(lbyte & 15);
+      const int qv = (nib | (int)(((hbyte >> (2 * j)) & 3) << 4)) - 32;
+      v[i] = (i < 16 ? s0 : s1) * (float)qv;
+    }
+  } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
+    const int b32 = 2 * kc + half;
+    const float d = scale_field_to_float(__ldg(reinterpret_cast<const uint16_t*>(u.unit + 256 + 2 * b32)));
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * b32)), b = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * b32 + 16));
+    const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = d * (float)(int)(int8_t)((qs[i >> 2] >> (8 * (i & 3))) & 0xFF);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    w[c] = make_uint4(pack_h2(v[8 * c], v[8 * c + 1]), pack_h2(v[8 * c + 2], v[8 * c + 3]), pack_h2(v[8 * c + 4], v[8 * c + 5]),
+                      pack_h2(v[8 * c + 6], v[8 * c + 7]));
+}
+
+struct TcShared {
+  unsigned long long mma_bar[2];  // the MMAs that read stage s have completed
+  unsigned long long done_bar;    // all MMAs of the tile have completed
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tc_fail(const TcParams& p, TcShared* sh) {
+  sh->abort_flag = 1;
+  if (p.error_flag) *reinterpret_cast<volatile int*>(p.error_flag) = 1;
+}
+
+// grid = (128-row tiles over all segments, token tiles of NT); 256 threads.
+// dynamic shared memory (1024-byte aligned): 2 x (A tile 16 KB + B tile NT x 128 bytes)
+__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT) { return 1024 + 2 * ((size_t)TC_M * 128 + (size_t)NT * 128); }
+
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
+  extern __shared__ uint8_t tc_smem_raw[];
+  __shared__ TcShared sh;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+  const size_t stage_bytes = (size_t)TC_M * 128 + (size_t)p.NT * 128;
+  // ---- which rows, which tokens ----
+  int seg = 0, mt = blockIdx.x;
+  while (seg + 1 < p.nseg && mt >= (p.seg[seg].rows + TC_M - 1) / TC_M) { mt -= (p.seg[seg].rows + TC_M - 1) / TC_M; ++seg; }
+  const GemvSeg& sg = p.seg[seg];
+  const int row0 = mt * TC_M;             // first image row of the tile within the segment
+  const int t0 = blockIdx.y * p.NT;       // first token of the tile
+  if (tid == 0) {
+    mbar_init(&sh.mma_bar[0], 1);
+    mbar_init(&sh.mma_bar[1], 1);
+    mbar_init(&sh.done_bar, 1);
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tc_alloc(&sh.tmem_base, p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = sh.tmem_base;
+  const uint32_t idesc = tc_idesc(p.NT);
+
+  const int my_row = tid & (TC_M - 1), my_half = tid >> 7;  // this thread dequantises 32 elements of one row per step
+  const int irow = min(row0 + my_row, sg.rows - 1);         // rows past the segment repeat the last one; their results are dropped
+  const int nsteps = p.K / TC_KC;
+  for (int step = 0; step < nsteps; ++step) {
+    const int buf = step & 1;
+    uint8_t* A = smem + buf * stage_bytes;
+    uint8_t* B = A + TC_M * 128;
+    // the MMAs that read this stage two steps ago must be done before it is overwritten
+    if (step >= 2) {
+      if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.mma_bar[buf], ((step >> 1) - 1) & 1)) tc_fail(p, &sh);
+    }
+    const int blk = step >> 2, kc = step & 3;
+    {
+      const TcUnit u = tc_locate(p, sg, irow, blk);
+      uint4 w[4];
+      tc_dequant32(sg.type, u, kc, my_half, w);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + c)) = w[c];
+    }
+    for (int idx = tid; idx < p.NT * 8; idx += TC_THREADS) {
+      const int r = idx >> 3, c = idx & 7;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (t0 + r < p.T) v = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + r) * p.K + (size_t)step * TC_KC + 8 * c));
+      *reinterpret_cast<uint4*>(B + tc_swz(r, c)) = v;
+    }
+    // generic-proxy stores -> visible to the tensor core's (async proxy) reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t a0 = smem_u32(A), b0 = smem_u32(B);
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)
+        tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (step | k4) ? 1u : 0u);
+      tc_commit(&sh.mma_bar[buf]);
+      if (step == nsteps - 1) tc_commit(&sh.done_bar);
+    }
+  }
+  // ---- epilogue: warp w reads TMEM lanes 32*(w & 3) .. +31 (= weight rows), the two warp groups split the tokens ----
+  if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.done_bar, 0)) tc_fail(p, &sh);
+  tc_fence_after();
+  if (!*(volatile int*)&sh.abort_flag) {
+    const int r_in_tile = 32 * (warp & 3) + lane;
+    const int row_img = row0 + r_in_tile;
+    const bool row_ok = row_img < sg.rows;
+    const int ncol_half = p.NT / 2;
+    const int c_begin = (warp >> 2) * ncol_half;
+    for (int c0 = c_begin; c0 < c_begin + ncol_half; c0 += 8) {
+      float v[8];
+      tc_ld8(tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = t0 + c0 + j;
+        const bool ok = row_ok && t < p.T;
+        const float tot = v[j];
+        if (p.epi == EPI_SWIGLU) {
+          // image rows: eight gate rows then the same eight up rows (reference model.cpp:734-735, batch form
+          // cpu_batch_processor.cpp:252-256: (g / (1 + exp(-g))) * u)
+          const float up = __shfl_sync(0xffffffffu, tot, (lane & 23) + 8);
+          if (ok && (r_in_tile & 15) < 8) {
+            const int orow = (row_img >> 4) * 8 + (r_in_tile & 7);
+            p.y[(size_t)t * p.y_stride + orow] = (tot / (1.0f + expf(-tot))) * up;
+          }
+        } else {
+          const float other = __shfl_xor_sync(0xffffffffu, tot, 1);
+          if (ok) {
+            if (p.epi == EPI_RESID) {
+              const float* rs = (p.resid ? p.resid : p.y) + (size_t)t * p.y_stride + row_img;
+              p.y[(size_t)t * p.y_stride + row_img] = *rs + tot;
+            } else if (p.epi == EPI_QKV_ROPE) {
+              float o = tot;
+              if (seg < 2) {
+                const int pos = p.positions[t];
+                if (pos >= 0 && pos < p.max_pos) {
+                  const int i = (row_img % p.head_dim) >> 1;
+                  const float2 cs = *reinterpret_cast<const float2*>(p.rope + ((size_t)pos * (p.head_dim >> 1) + i) * 2);
+                  o = (row_img & 1) ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(tot, cs.x))
+                                    : __fsub_rn(__fmul_rn(tot, cs.x), __fmul_rn(other, cs.y));
+                }
+              }
+              float* dst = seg == 0 ? p.y + (size_t)t * p.y_stride + row_img
+                                    : p.y2 + (size_t)t * p.y2_stride + (seg == 2 ? p.seg[1].rows : 0) + row_img;
+              *dst = o;
+            } else {
+              p.y[(size_t)t * p.y_stride + row_img] = tot;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc_dealloc(tmem_d, p.tmem_cols);
+}
+
+// x16[t][k] = fp16(x[t][k]) or, with norm weights, fp16(RMSNorm(x[t])[k]) (reference rmsnorm_batch_cpu,
+// utils.cpp:613-646: f = 1/sqrtf(mean(x^2) + eps), out = x * f * w). One block per token.
+__global__ void to_half_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ norm_w, float eps, int K,
+                               __half* __restrict__ out) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const float* xr = x + (size_t)t * x_stride;
+  float f = 1.0f;
+  if (norm_w) {
+    float ss = 0.f;
+    for (int i = tid; i < K; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < nwarps; ++w) tot += red[w];
+      red[32] = 1.0f / sqrtf(tot / (float)K + eps);
+    }
+    __syncthreads();
+    f = red[32];
+  }
+  for (int i = tid; i < K; i += blockDim.x) out[(size_t)t * K + i] = __float2half_rn(norm_w ? xr[i] * f * norm_w[i] : xr[i]);
+}
+
+}  // namespace b200
