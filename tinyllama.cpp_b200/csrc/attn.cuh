@@ -39,6 +39,7 @@ struct AttnParams {
   int out_stride;
   float att_scale;
   unsigned long long* trace;  // optional step-trace record: entry, inputs ready, this CTA's partials written, end
+  int cached_new;        // 1: the row of the newest position is already in the cache (prompt ingestion): read it like any other row
 };
 
 constexpr int ATTN_GROUP_THREADS = 128;
@@ -114,8 +115,9 @@ __device__ void attn_item(const AttnParams& prm, int split, int h, int b, float*
   const int lane = gtid & 31, warp = gtid >> 5;
   constexpr int nwarps = ATTN_GROUP_THREADS / 32;
   const int hd = HD ? HD : prm.hd, G = prm.nq / prm.nkv, kvh = h / G;
-  const int pos = prm.positions[b], slot = prm.slots[b];
-  const int T = pos + 1;
+  const int pos_real = prm.positions[b], slot = prm.slots[b];
+  const int T = pos_real + 1;
+  const int pos = prm.cached_new ? -1 : pos_real;  // the position whose K/V row comes from kv_new rather than from the cache
   int chunk = (T + prm.nsplit - 1) / prm.nsplit;
   chunk = (chunk + 31) & ~31;
   const int t0 = split * chunk, t1 = min(T, t0 + chunk);
@@ -341,6 +343,31 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
   attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd, sm, 1);
   if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
   trace_stamp(rec, 3);
+}
+
+// Prompt ingestion: appends the K and V rows of n tokens to the cache before their attention runs
+// (same arithmetic as the append inside attn_item). grid = (tokens, kv heads, 2: K | V), one warp each.
+__global__ void kv_append_kernel(const float* __restrict__ kv_new, int kvn_stride, const int* __restrict__ positions,
+                                 const int* __restrict__ slots, int nkv, int hd, int max_ctx, int kv_i8, void* k_cache, void* v_cache,
+                                 float* k_scale, float* v_scale) {
+  const int t = blockIdx.x, kvh = blockIdx.y, which = blockIdx.z, lane = threadIdx.x;
+  const float* src = kv_new + (size_t)t * kvn_stride + (which ? nkv * hd : 0) + kvh * hd;
+  const size_t crow = ((size_t)slots[t] * nkv + kvh) * max_ctx + positions[t];
+  void* cache = which ? v_cache : k_cache;
+  if (kv_i8) {
+    float amax = 0.f;
+    for (int d = lane; d < hd; d += 32) amax = fmaxf(amax, fabsf(src[d]));
+    amax = warp_max(amax);
+    const float scale = ((double)amax > 1e-8) ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    for (int d = lane; d < hd; d += 32) {
+      float r = roundf(__fdiv_rn(src[d], scale));
+      r = fmaxf(-127.0f, fminf(127.0f, r));
+      reinterpret_cast<int8_t*>(cache)[crow * hd + d] = (int8_t)r;
+    }
+    if (lane == 0) (which ? v_scale : k_scale)[crow] = scale;
+  } else {
+    for (int d = lane; d < hd; d += 32) reinterpret_cast<float*>(cache)[crow * hd + d] = src[d];
+  }
 }
 
 inline size_t attn_smem_bytes(int hd, int max_ctx, int nsplit, int /*nwarps*/) {

@@ -153,7 +153,8 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   static bool attr_done = false;
   if (!attr_done) {
-    CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
+    CK(cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(64)));
+    CK(cudaFuncSetAttribute(gemm_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
     attr_done = true;
   }
   const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
@@ -168,7 +169,8 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   for (int s = 0; s < p.nseg; ++s) p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
   p.error_flag = e->d_error;
   dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT);
-  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
+  if (NT <= 64) gemm_tc_kernel<2><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
+  else gemm_tc_kernel<8><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
   CK(cudaGetLastError());
 }
 
@@ -263,6 +265,34 @@ static int tp_reduce_add(b200_engine* e, int batch, cudaStream_t st) {
   return 2;
 }
 
+// One fused linear layer of the step: the matvec kernel (one launch column per sequence), or, for
+// large batches on a single GPU, fp16 conversion (+RMSNorm) followed by the tensor-core matmul.
+// Returns the number of launches; *grid_out = partial-argmax parts per sequence (lm_head only).
+static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t st, bool use_tc, int* grid_out = nullptr,
+                         void* x16_buf = nullptr) {
+  if (!use_tc) {
+    const int g = launch_gemv(e, p, batch, st);
+    if (grid_out) *grid_out = g;
+    return 1;
+  }
+  __half* x16 = static_cast<__half*>(x16_buf ? x16_buf : e->d_x16);
+  to_half_kernel<<<batch, 256, 0, st>>>(p.x, p.x_stride, p.norm_w, p.eps, p.K, x16);
+  CK(cudaGetLastError());
+  TcParams t{};
+  for (int s = 0; s < p.nseg; ++s) t.seg[s] = p.seg[s];
+  t.nseg = p.nseg; t.K = p.K; t.x16 = x16; t.T = batch; t.epi = p.epi; t.y = p.y; t.y_stride = p.y_stride; t.y2 = p.y2;
+  t.y2_stride = p.y2_stride; t.resid = p.resid; t.rope = p.rope; t.positions = p.positions; t.head_dim = p.head_dim; t.max_pos = p.max_pos;
+  launch_gemm_tc(e, t, st);
+  int n = 2;
+  if (p.amax_val) {  // lm_head: the matvec kernel leaves argmax partials; here a small kernel scans the logits
+    argmax_rows_kernel<<<batch, 256, 0, st>>>(p.y, p.y_stride, p.amax_val, p.amax_idx);
+    CK(cudaGetLastError());
+    if (grid_out) *grid_out = 1;
+    ++n;
+  }
+  return n;
+}
+
 // The launch sequence of one decode step for `batch` sequences (also what gets captured).
 // Per layer: [RMSNorm + QKV + RoPE] -> [KV append + attention] -> [O proj + residual] ->
 // [RMSNorm + gate/up + SwiGLU] -> [down proj + residual]; then [RMSNorm + lm_head + argmax
@@ -278,6 +308,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   // new stream to the other of two buffers. There are 2L exchanges per step, so the stream is back
   // in d_h when the step ends.
   const bool peer = tp && e->use_peer;
+  const bool use_tc = !tp && batch >= e->gemm_min_batch;
   const size_t slots_bytes = (size_t)2 * e->tp_size * e->max_seqs * H * sizeof(float);
   auto slot_of = [&](void* region, int k, int src) {
     return static_cast<float*>(region) + ((size_t)(k & 1) * e->tp_size + src) * e->max_seqs * H;
@@ -319,8 +350,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.y = e->d_q; p.y_stride = e->Hq; p.y2 = e->d_kvnew; p.y2_stride = 2 * KVD;
       p.rope = e->rope; p.positions = e->d_positions; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
       p.trace = trace_rec(e, launches);
-      launch_gemv(e, p, batch, st);
-      ++launches;
+      launches += launch_linear(e, p, batch, st, use_tc);
     }
     {
       AttnParams a{};
@@ -340,8 +370,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
       if (peer) as_producer(p, 2 * l);
       p.trace = trace_rec(e, launches);
-      launch_gemv(e, p, batch, st);
-      ++launches;
+      launches += launch_linear(e, p, batch, st, use_tc);
       if (tp && !peer) launches += tp_reduce_add(e, batch, st);
     }
     {
@@ -351,8 +380,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       if (peer) as_consumer(p);
       p.y = e->d_act; p.y_stride = F;
       p.trace = trace_rec(e, launches);
-      launch_gemv(e, p, batch, st);
-      ++launches;
+      launches += launch_linear(e, p, batch, st, use_tc);
     }
     {
       GemvParams p{};
@@ -360,8 +388,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.y = tp ? e->d_partial : e->d_h; p.y_stride = H;
       if (peer) as_producer(p, 2 * l + 1);
       p.trace = trace_rec(e, launches);
-      launch_gemv(e, p, batch, st);
-      ++launches;
+      launches += launch_linear(e, p, batch, st, use_tc);
       if (tp && !peer) launches += tp_reduce_add(e, batch, st);
     }
   }
@@ -376,8 +403,8 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     p.amax_val = tp ? e->d_amax_val + half : e->d_amax_val; p.amax_idx = tp ? e->d_amax_idx + half : e->d_amax_idx;
     p.amax_row_offset = e->tp_rank * e->Vl;
     p.trace = trace_rec(e, launches);
-    const int grid = launch_gemv(e, p, batch, st);
-    ++launches;
+    int grid = 0;
+    launches += launch_linear(e, p, batch, st, use_tc, &grid);
     if (tp) {
       Nccl& n = Nccl::get();
       n.check(n.AllGather(e->d_logits_local, e->d_logits, (size_t)batch * e->Vl, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
@@ -396,6 +423,104 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     ++launches;
   }
   return launches;
+}
+
+// ---- prompt ingestion on the tensor cores -------------------------------------------------------
+// forward_device_batch_prefill (reference model.cpp:1526-1862) / CPUBatchProcessor::forward_cpu_batch
+// (cpu_batch_processor.cpp:11-281): all tokens of a chunk go through every layer together. Linear
+// layers = fp16 conversion (+RMSNorm, batch form: eps as configured) + tcgen05 matmul; the chunk's
+// K/V rows are appended to the cache first, then every token runs the decode-attention kernel over
+// the cache rows up to and including its own position (causal). Only the last token's logits are
+// computed (the reference computes all rows and keeps the last, model.cpp:1094-1156).
+constexpr int PF_CHUNK = 256;
+
+static void ensure_prefill_buffers(b200_engine* e) {
+  if (e->pf_cap) return;
+  const int T = PF_CHUNK;
+  e->pf_ints = dev_alloc<int>(e, (size_t)3 * T);
+  e->pf_h = dev_alloc<float>(e, (size_t)T * e->H);
+  e->pf_q = dev_alloc<float>(e, (size_t)T * e->H);
+  e->pf_kvnew = dev_alloc<float>(e, (size_t)T * 2 * e->KVD);
+  e->pf_attn = dev_alloc<float>(e, (size_t)T * e->H);
+  e->pf_act = dev_alloc<float>(e, (size_t)T * e->F);
+  e->pf_x16 = dev_alloc<uint16_t>(e, (size_t)T * std::max(e->H, e->F));
+  size_t items = 0;
+  for (int t = 1; t <= T; ++t) items = std::max(items, (size_t)t * e->nq * attn_nsplit(e, t));
+  e->pf_part_o = dev_alloc<float>(e, items * e->hd);
+  e->pf_part_ml = dev_alloc<float>(e, items * 2);
+  e->pf_tickets = dev_alloc<int>(e, (size_t)T * e->nq);
+  CK(cudaMemset(e->pf_tickets, 0, (size_t)T * e->nq * 4));
+  e->pf_cap = T;
+}
+
+// One chunk of T <= PF_CHUNK prompt tokens of sequence `slot` at positions start .. start+T-1.
+// last: also leave the logits of the chunk's last token in e->d_logits.
+static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, int start, bool last) {
+  ensure_prefill_buffers(e);
+  cudaStream_t st = e->stream;
+  const int H = e->H, F = e->F, KVD = e->KVD;
+  std::vector<int> meta((size_t)3 * T);
+  for (int t = 0; t < T; ++t) { meta[t] = ids[t]; meta[T + t] = start + t; meta[2 * T + t] = slot; }
+  CK(cudaMemcpyAsync(e->pf_ints, meta.data(), meta.size() * 4, cudaMemcpyHostToDevice, st));
+  CK(cudaStreamSynchronize(st));  // meta is a stack-lifetime buffer
+  const int* d_tok = e->pf_ints;
+  const int* d_pos = e->pf_ints + T;
+  const int* d_slot = e->pf_ints + 2 * T;
+  const float eps = e->desc.rms_norm_eps;  // rmsnorm_batch_cpu form (utils.cpp:613-646)
+  const bool i8 = e->desc.kv_dtype == B200_KV_I8;
+  embed_kernel<<<T, 256, 0, st>>>(d_tok, e->tok_embd.f32(), e->pf_h, H, e->V);
+  CK(cudaGetLastError());
+  const int nsplit = attn_use_cluster() ? 1 : attn_nsplit(e, T);
+  for (int l = 0; l < e->L; ++l) {
+    const LayerW& w = e->layers[l];
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wq); p.seg[1] = seg_of(w.wk); p.seg[2] = seg_of(w.wv); p.nseg = 3;
+      p.K = H; p.x = e->pf_h; p.x_stride = H; p.norm_w = w.attn_norm.f32(); p.eps = eps; p.epi = EPI_QKV_ROPE;
+      p.y = e->pf_q; p.y_stride = e->Hq; p.y2 = e->pf_kvnew; p.y2_stride = 2 * KVD;
+      p.rope = e->rope; p.positions = d_pos; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
+      launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+    }
+    kv_append_kernel<<<dim3(T, e->nkv, 2), 32, 0, st>>>(e->pf_kvnew, 2 * KVD, d_pos, d_slot, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0, w.k_cache,
+                                                        w.v_cache, w.k_scale, w.v_scale);
+    CK(cudaGetLastError());
+    {
+      AttnParams a{};
+      a.q = e->pf_q; a.kv_new = e->pf_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
+      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+      a.positions = d_pos; a.slots = d_slot;
+      a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
+      a.part_o = e->pf_part_o; a.part_ml = e->pf_part_ml; a.tickets = e->pf_tickets;
+      a.out = e->pf_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      a.cached_new = 1;
+      launch_attention(a, T, i8, false, true, st);
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->pf_attn; p.x_stride = e->Hq; p.epi = EPI_RESID;
+      p.y = e->pf_h; p.y_stride = H;
+      launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wgu); p.nseg = 1;
+      p.K = H; p.x = e->pf_h; p.x_stride = H; p.norm_w = w.ffn_norm.f32(); p.eps = eps; p.epi = EPI_SWIGLU;
+      p.y = e->pf_act; p.y_stride = F;
+      launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+    }
+    {
+      GemvParams p{};
+      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->pf_act; p.x_stride = F; p.epi = EPI_RESID;
+      p.y = e->pf_h; p.y_stride = H;
+      launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+    }
+  }
+  if (last) {  // final norm + lm_head for the last token only, on the matvec kernel
+    GemvParams p{};
+    p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->pf_h + (size_t)(T - 1) * H; p.x_stride = H;
+    p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE; p.y = e->d_logits; p.y_stride = e->V;
+    launch_gemv(e, p, 1, st);
+  }
 }
 
 static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {

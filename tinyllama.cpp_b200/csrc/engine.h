@@ -86,6 +86,20 @@ struct b200_engine {
   float* d_kvnew = nullptr;
   float* d_attn = nullptr;
   float* d_act = nullptr;
+  void* d_x16 = nullptr;        // fp16 activations of the tensor-core path, [max_seqs][max(H, F)]
+  // prompt ingestion through the tensor-core matmul: buffers for one chunk of tokens, allocated at the first use
+  int pf_cap = 0;
+  int* pf_ints = nullptr;       // tokens | positions | slots, pf_cap each
+  float* pf_h = nullptr;
+  float* pf_q = nullptr;
+  float* pf_kvnew = nullptr;
+  float* pf_attn = nullptr;
+  float* pf_act = nullptr;
+  void* pf_x16 = nullptr;
+  float* pf_part_o = nullptr;
+  float* pf_part_ml = nullptr;
+  int* pf_tickets = nullptr;
+  int gemm_min_batch = 16;      // batches at least this large take the tensor-core matmul (B200_GEMM_MIN_BATCH)
   float* d_logits = nullptr;
   float* d_amax_val = nullptr;
   int* d_amax_idx = nullptr;

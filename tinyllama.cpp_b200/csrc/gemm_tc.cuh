@@ -126,18 +126,55 @@ __device__ __forceinline__ TcUnit tc_locate(const TcParams& p, const GemvSeg& sg
   return u;
 }
 
-// Dequantises 32 consecutive elements of a row: elements [64*kc + 32*half, +32) of 256-element
-// block `u`, to fp16, into four 16-byte chunks w[0..3] (eight halves each).
+// The packed bytes of one 256-element block that one thread (row, half) needs for the block's four
+// K steps, fetched one block ahead of their use so that the loads overlap the previous block's
+// dequantisation and MMAs:
+//   Q4_K: r[0] = d, dmin, 12 scale bytes; r[1..8] = the 128 nibble bytes
+//   Q6_K: r[0..3] = ql[64h' + 32*half ..+32) for h' = 0, 1; r[4..7] = qh (64 bytes); r[8] = scales; r[9].x = d
+//   Q8_0: r[2kc .. 2kc+1] = quants of 32-block 2kc + half; r[8] = the eight fp16 d
+struct TcRaw {
+  uint4 r[10];
+};
+
+__device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, TcRaw& t) {
+  if (type == T_Q4_K) {
+#pragma unroll
+    for (int i = 0; i < 9; ++i) t.r[i] = __ldg(reinterpret_cast<const uint4*>(u.unit) + i);
+  } else if (type == T_Q6_K) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      t.r[2 * hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half));
+      t.r[2 * hh + 1] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half + 16));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) t.r[4 + i] = __ldg(reinterpret_cast<const uint4*>(u.unit + 128) + i);
+    t.r[8] = __ldg(reinterpret_cast<const uint4*>(u.unit + 192));
+    t.r[9].x = __ldg(reinterpret_cast<const uint16_t*>(u.d));
+  } else {
+#pragma unroll
+    for (int kc = 0; kc < 4; ++kc) {
+      t.r[2 * kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half)));
+      t.r[2 * kc + 1] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half) + 16));
+    }
+    t.r[8] = __ldg(reinterpret_cast<const uint4*>(u.unit + 256));
+  }
+}
+
+__device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// Dequantises 32 consecutive elements of a row: elements [64*kc + 32*half, +32) of the block held
+// in `t`, to fp16, into four 16-byte chunks w[0..3] (eight halves each). kc is a compile-time
+// constant at every call site (the K steps of a block are unrolled).
 // Formulas: reference dequantize_q4_k_m / dequantize_q6_k / dequantize_q8_0_block
 // (quantization.cpp:171-266, 1047-1052) with the products fused (the matmul contract is a tolerance).
-__device__ __forceinline__ void tc_dequant32(int type, const TcUnit& u, int kc, int half, uint4 (&w)[4]) {
+__device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, int half, uint4 (&w)[4]) {
   float v[32];
   if (type == T_Q4_K) {
-    const uint4 h = __ldg(reinterpret_cast<const uint4*>(u.unit));
+    const uint4 h = t.r[0];
     const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
     const int sb = 2 * kc + half;  // 32-element sub-block
     // get_scale_min_k4 (quantization.cpp:145-155) on the 12 scale bytes h.y h.z h.w
-    auto q = [&](int i) -> int {  // byte i of the 12 scale bytes
+    auto q = [&](int i) -> int {
       const uint32_t wv = i < 4 ? h.y : (i < 8 ? h.z : h.w);
       return (int)((wv >> (8 * (i & 3))) & 0xFF);
     };
@@ -150,40 +187,38 @@ __device__ __forceinline__ void tc_dequant32(int type, const TcUnit& u, int kc, 
       mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
     }
     const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc));
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc + 16));
-    const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const uint32_t byte = (qs[i >> 2] >> (8 * (i & 3))) & 0xFF;
+      const uint32_t word = u4_word(t.r[1 + 2 * kc + (i >> 4)], (i >> 2) & 3);
+      const uint32_t byte = (word >> (8 * (i & 3))) & 0xFF;
       const float qv = (float)(half ? (byte >> 4) : (byte & 15));
       v[i] = fmaf(d1, qv, -m1);
     }
   } else if (type == T_Q6_K) {
     const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
-    const float d = half_bits_to_float(__ldg(reinterpret_cast<const uint16_t*>(u.d)));
-    const uint8_t* ql = u.unit + 64 * hh + 32 * (j & 1);
-    const uint8_t* qh = u.unit + 128 + 32 * hh;
-    const int8_t* sc = reinterpret_cast<const int8_t*>(u.unit + 192) + 8 * hh + 2 * j;
-    const uint4 la = __ldg(reinterpret_cast<const uint4*>(ql)), lb = __ldg(reinterpret_cast<const uint4*>(ql + 16));
-    const uint4 ha = __ldg(reinterpret_cast<const uint4*>(qh)), hb = __ldg(reinterpret_cast<const uint4*>(qh + 16));
-    const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-    const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
-    const float s0 = d * (float)sc[0], s1 = d * (float)sc[1];
+    const float d = half_bits_to_float((uint16_t)t.r[9].x);
+    // sub-block scales 8hh + 2j and + 1 (signed bytes)
+    const uint32_t sw = u4_word(t.r[8], 2 * hh + (j >> 1));
+    const float s0 = d * (float)(int)(int8_t)((sw >> (16 * (j & 1))) & 0xFF);
+    const float s1 = d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8)) & 0xFF);
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const uint32_t lbyte = (lw[i >> 2] >> (8 * (i & 3))) & 0xFF, hbyte = (hw[i >> 2] >> (8 * (i & 3))) & 0xFF;
+      const uint32_t lword = u4_word(t.r[2 * hh + (i >> 4)], (i >> 2) & 3);
+      const uint32_t hword = u4_word(t.r[4 + 2 * hh + (i >> 4)], (i >> 2) & 3);
+      const uint32_t lbyte = (lword >> (8 * (i & 3))) & 0xFF, hbyte = (hword >> (8 * (i & 3))) & 0xFF;
       const int nib = (j >> 1) ? (int)(lbyte >> 4) : (int)(lbyte & 15);
       const int qv = (nib | (int)(((hbyte >> (2 * j)) & 3) << 4)) - 32;
       v[i] = (i < 16 ? s0 : s1) * (float)qv;
     }
   } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
     const int b32 = 2 * kc + half;
-    const float d = scale_field_to_float(__ldg(reinterpret_cast<const uint16_t*>(u.unit + 256 + 2 * b32)));
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * b32)), b = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * b32 + 16));
-    const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t dwv = u4_word(t.r[8], b32 >> 1);
+    const float d = scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF));
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = d * (float)(int)(int8_t)((qs[i >> 2] >> (8 * (i & 3))) & 0xFF);
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t word = u4_word(t.r[2 * kc + (i >> 4)], (i >> 2) & 3);
+      v[i] = d * (float)(int)(int8_t)((word >> (8 * (i & 3))) & 0xFF);
+    }
   }
 #pragma unroll
   for (int c = 0; c < 4; ++c)
@@ -207,7 +242,9 @@ __device__ __forceinline__ void tc_fail(const TcParams& p, TcShared* sh) {
 // dynamic shared memory (1024-byte aligned): 2 x (A tile 16 KB + B tile NT x 128 bytes)
 __host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT) { return 1024 + 2 * ((size_t)TC_M * 128 + (size_t)NT * 128); }
 
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p) {
+// BMAX: 16-byte activation chunks a thread moves per step (2: token tiles up to 64, two CTAs per SM; 8: up to 256).
+template <int BMAX>
+__global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(const TcParams p) {
   extern __shared__ uint8_t tc_smem_raw[];
   __shared__ TcShared sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -235,42 +272,63 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 
   const int my_row = tid & (TC_M - 1), my_half = tid >> 7;  // this thread dequantises 32 elements of one row per step
   const int irow = min(row0 + my_row, sg.rows - 1);         // rows past the segment repeat the last one; their results are dropped
-  const int nsteps = p.K / TC_KC;
-  for (int step = 0; step < nsteps; ++step) {
-    const int buf = step & 1;
-    uint8_t* A = smem + buf * stage_bytes;
-    uint8_t* B = A + TC_M * 128;
-    // the MMAs that read this stage two steps ago must be done before it is overwritten
-    if (step >= 2) {
-      if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.mma_bar[buf], ((step >> 1) - 1) & 1)) tc_fail(p, &sh);
-    }
-    const int blk = step >> 2, kc = step & 3;
-    {
-      const TcUnit u = tc_locate(p, sg, irow, blk);
-      uint4 w[4];
-      tc_dequant32(sg.type, u, kc, my_half, w);
+  const int nsteps = p.K / TC_KC, nblocks = p.K / 256;
+  const int nb_chunks = p.NT * 8;
+  auto fetch_b = [&](int step, uint4 (&bv)[BMAX]) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + c)) = w[c];
+    for (int i = 0; i < BMAX; ++i) {
+      const int idx = tid + i * TC_THREADS;
+      bv[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (idx < nb_chunks && t0 + (idx >> 3) < p.T)
+        bv[i] = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + (idx >> 3)) * p.K + (size_t)step * TC_KC + 8 * (idx & 7)));
     }
-    for (int idx = tid; idx < p.NT * 8; idx += TC_THREADS) {
-      const int r = idx >> 3, c = idx & 7;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (t0 + r < p.T) v = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + r) * p.K + (size_t)step * TC_KC + 8 * c));
-      *reinterpret_cast<uint4*>(B + tc_swz(r, c)) = v;
-    }
-    // generic-proxy stores -> visible to the tensor core's (async proxy) reads
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t a0 = smem_u32(A), b0 = smem_u32(B);
+  };
+  TcRaw cur, nxt;
+  tc_fetch(sg.type, tc_locate(p, sg, irow, 0), my_half, cur);
+  uint4 bcur[BMAX], bnxt[BMAX];
+  fetch_b(0, bcur);
+#pragma unroll 1
+  for (int blk = 0; blk < nblocks; ++blk) {
+    if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk + 1), my_half, nxt);  // lands while this block is worked on
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4)
-        tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (step | k4) ? 1u : 0u);
-      tc_commit(&sh.mma_bar[buf]);
-      if (step == nsteps - 1) tc_commit(&sh.done_bar);
+    for (int kc = 0; kc < 4; ++kc) {
+      const int step = 4 * blk + kc;
+      const int buf = kc & 1;
+      uint8_t* A = smem + buf * stage_bytes;
+      uint8_t* B = A + TC_M * 128;
+      if (step + 1 < nsteps) fetch_b(step + 1, bnxt);
+      // the MMAs that read this stage two steps ago must be done before it is overwritten
+      if (step >= 2) {
+        if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.mma_bar[buf], ((step >> 1) - 1) & 1)) tc_fail(p, &sh);
+      }
+      {
+        uint4 w[4];
+        tc_dequant32(sg.type, cur, kc, my_half, w);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + c)) = w[c];
+      }
+#pragma unroll
+      for (int i = 0; i < BMAX; ++i) {
+        const int idx = tid + i * TC_THREADS;
+        if (idx < nb_chunks) *reinterpret_cast<uint4*>(B + tc_swz(idx >> 3, idx & 7)) = bcur[i];
+      }
+      // generic-proxy stores -> visible to the tensor core's (async proxy) reads
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(A), b0 = smem_u32(B);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (step | k4) ? 1u : 0u);
+        tc_commit(&sh.mma_bar[buf]);
+        if (step == nsteps - 1) tc_commit(&sh.done_bar);
+      }
+#pragma unroll
+      for (int i = 0; i < BMAX; ++i) bcur[i] = bnxt[i];
     }
+    cur = nxt;
   }
   // ---- epilogue: warp w reads TMEM lanes 32*(w & 3) .. +31 (= weight rows), the two warp groups split the tokens ----
   if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.done_bar, 0)) tc_fail(p, &sh);

@@ -74,6 +74,36 @@ __global__ void select_kernel(const SelectParams p) {
   }
 }
 
+// First maximum of each row of logits [batch][vocab] (reference api.cpp:134-136), in the partial
+// format select_kernel merges (one part per sequence). One block per sequence.
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ amax_val, int* __restrict__ amax_idx) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const float* row = logits + (size_t)b * vocab;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+#pragma unroll 1
+  for (int i = tid; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv) { bv = v; bi = i; }  // increasing i per thread: the first maximum stays
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < nwarps; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    amax_val[b] = bv;
+    amax_idx[b] = bi;
+  }
+}
+
 // h[i] += partial[i]: the residual add after a tensor-parallel all-reduce.
 __global__ void add_inplace_kernel(float* __restrict__ h, const float* __restrict__ partial, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
