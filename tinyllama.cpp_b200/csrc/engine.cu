@@ -168,7 +168,8 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   p.ntiles_m = 0;
   for (int s = 0; s < p.nseg; ++s) p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
   p.error_flag = e->d_error;
-  dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT);
+  if (p.ksplit < 1) { p.ksplit = 1; p.kblocks = p.K / 256; }
+  dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT, p.ksplit);
   if (NT <= 64) gemm_tc_kernel<2><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
   else gemm_tc_kernel<8><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
   CK(cudaGetLastError());
@@ -282,8 +283,26 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
   for (int s = 0; s < p.nseg; ++s) t.seg[s] = p.seg[s];
   t.nseg = p.nseg; t.K = p.K; t.x16 = x16; t.T = batch; t.epi = p.epi; t.y = p.y; t.y_stride = p.y_stride; t.y2 = p.y2;
   t.y2_stride = p.y2_stride; t.resid = p.resid; t.rope = p.rope; t.positions = p.positions; t.head_dim = p.head_dim; t.max_pos = p.max_pos;
-  launch_gemm_tc(e, t, st);
   int n = 2;
+  // Few row tiles (O and down projections: 32 for a 4096-row matrix) leave most SMs idle: split K over
+  // up to 8 CTAs per tile, partial outputs summed in order by a small kernel (with the residual).
+  const int ctas = (int)((p.seg[0].rows + TC_M - 1) / TC_M) * ((batch + TC_MAX_N - 1) / TC_MAX_N);
+  const int nblk = p.K / 256;
+  int ks = 1;
+  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 256) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
+  if (ks > 1) {
+    if (!e->d_tc_part) e->d_tc_part = dev_alloc<float>(e, (size_t)8 * 256 * e->H);
+    t.ksplit = ks; t.kblocks = (nblk + ks - 1) / ks;
+    t.ksplit = (nblk + t.kblocks - 1) / t.kblocks;  // no empty split
+    t.epi = EPI_STORE; t.y = e->d_tc_part; t.y_stride = p.seg[0].rows;
+    launch_gemm_tc(e, t, st);
+    const size_t nel = (size_t)batch * p.seg[0].rows;
+    splitk_reduce_kernel<<<(unsigned)std::min<size_t>((nel + 255) / 256, 1184), 256, 0, st>>>(e->d_tc_part, t.ksplit, batch, p.seg[0].rows, p.resid, p.y, p.y_stride);
+    CK(cudaGetLastError());
+    ++n;
+  } else {
+    launch_gemm_tc(e, t, st);
+  }
   if (p.amax_val) {  // lm_head: the matvec kernel leaves argmax partials; here a small kernel scans the logits
     argmax_rows_kernel<<<batch, 256, 0, st>>>(p.y, p.y_stride, p.amax_val, p.amax_idx);
     CK(cudaGetLastError());

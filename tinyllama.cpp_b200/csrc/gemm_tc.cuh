@@ -49,6 +49,7 @@ struct TcParams {
   const int* positions;           // [T]
   int head_dim, max_pos;
   int ntiles_m;                   // 128-row tiles over all segments
+  int ksplit, kblocks;            // split-K: CTA z takes 256-element blocks [z*kblocks, (z+1)*kblocks) and stores to y + z*T*y_stride (EPI_STORE only)
   int* error_flag;
 };
 
@@ -272,7 +273,8 @@ __global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(
 
   const int my_row = tid & (TC_M - 1), my_half = tid >> 7;  // this thread dequantises 32 elements of one row per step
   const int irow = min(row0 + my_row, sg.rows - 1);         // rows past the segment repeat the last one; their results are dropped
-  const int nsteps = p.K / TC_KC, nblocks = p.K / 256;
+  const int blk0 = blockIdx.z * p.kblocks;
+  const int nblocks = min(p.K / 256 - blk0, p.kblocks), nsteps = 4 * nblocks;  // this CTA's share of K
   const int nb_chunks = p.NT * 8;
   auto fetch_b = [&](int step, uint4 (&bv)[BMAX]) {
 #pragma unroll
@@ -280,16 +282,16 @@ __global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(
       const int idx = tid + i * TC_THREADS;
       bv[i] = make_uint4(0u, 0u, 0u, 0u);
       if (idx < nb_chunks && t0 + (idx >> 3) < p.T)
-        bv[i] = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + (idx >> 3)) * p.K + (size_t)step * TC_KC + 8 * (idx & 7)));
+        bv[i] = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + (idx >> 3)) * p.K + (size_t)(4 * blk0 + step) * TC_KC + 8 * (idx & 7)));
     }
   };
   TcRaw cur, nxt;
-  tc_fetch(sg.type, tc_locate(p, sg, irow, 0), my_half, cur);
+  tc_fetch(sg.type, tc_locate(p, sg, irow, blk0), my_half, cur);
   uint4 bcur[BMAX], bnxt[BMAX];
   fetch_b(0, bcur);
 #pragma unroll 1
   for (int blk = 0; blk < nblocks; ++blk) {
-    if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk + 1), my_half, nxt);  // lands while this block is worked on
+    if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk0 + blk + 1), my_half, nxt);  // lands while this block is worked on
 #pragma unroll
     for (int kc = 0; kc < 4; ++kc) {
       const int step = 4 * blk + kc;
@@ -376,7 +378,7 @@ __global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(
                                     : p.y2 + (size_t)t * p.y2_stride + (seg == 2 ? p.seg[1].rows : 0) + row_img;
               *dst = o;
             } else {
-              p.y[(size_t)t * p.y_stride + row_img] = tot;
+              p.y[((size_t)blockIdx.z * p.T + t) * p.y_stride + row_img] = tot;
             }
           }
         }
@@ -386,6 +388,18 @@ __global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tc_dealloc(tmem_d, p.tmem_cols);
+}
+
+// Split-K epilogue: y[t][r] = (resid ? resid : y)[t][r] + sum_z part[z][t][r], z in order (deterministic).
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int ksplit, int T, int rows, const float* __restrict__ resid,
+                                     float* __restrict__ y, int y_stride) {
+  const size_t n = (size_t)T * rows;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / rows, r = i - t * rows;
+    float acc = (resid ? resid : y)[t * y_stride + r];
+    for (int z = 0; z < ksplit; ++z) acc += part[(size_t)z * n + i];
+    y[t * y_stride + r] = acc;
+  }
 }
 
 // x16[t][k] = fp16(x[t][k]) or, with norm weights, fp16(RMSNorm(x[t])[k]) (reference rmsnorm_batch_cpu,
