@@ -163,13 +163,34 @@ __device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, Tc
 
 __device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
+// Four bytes of `v` (values 0..255) as four fp16 numbers 1024 + byte, two per word: 0x6400 is
+// 1024.0 and an integer below 1024 in the low mantissa bits adds exactly. lo = bytes 0, 1; hi = bytes 2, 3.
+__device__ __forceinline__ void bytes_to_h2_biased(uint32_t v, uint32_t& lo, uint32_t& hi) {
+  lo = __byte_perm(v, 0x64646464u, 0x4140);  // [b0, 0x64, b1, 0x64]
+  hi = __byte_perm(v, 0x64646464u, 0x4342);  // [b2, 0x64, b3, 0x64]
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b), *reinterpret_cast<const __half2*>(&c));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_dup(float f) { return pack_h2(f, f); }
+
 // Dequantises 32 consecutive elements of a row: elements [64*kc + 32*half, +32) of the block held
 // in `t`, to fp16, into four 16-byte chunks w[0..3] (eight halves each). kc is a compile-time
-// constant at every call site (the K steps of a block are unrolled).
-// Formulas: reference dequantize_q4_k_m / dequantize_q6_k / dequantize_q8_0_block
-// (quantization.cpp:171-266, 1047-1052) with the products fused (the matmul contract is a tolerance).
+// constant at every call site (the K steps of a block are unrolled). The integers go to fp16
+// through the 1024 + byte trick (exact), the scale and offset are applied in fp16 pairs: about
+// two instructions per element. Formulas: reference dequantize_q4_k_m / dequantize_q6_k /
+// dequantize_q8_0_block (quantization.cpp:171-266, 1047-1052); the matmul contract is a tolerance.
 __device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, int half, uint4 (&w)[4]) {
-  float v[32];
+  uint32_t out[16];  // 32 halves, in element order
   if (type == T_Q4_K) {
     const uint4 h = t.r[0];
     const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
@@ -187,44 +208,55 @@ __device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, i
       sc = (q(sb + 4) & 0xF) | ((q(sb - 4) >> 6) << 4);
       mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
     }
-    const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
+    const uint32_t d1 = h2_dup(dm.x * (float)sc);
+    // (folding the 1024 bias into the offset would lose precision: 1024 * d1 dwarfs the result; it is subtracted first, exactly)
+    const uint32_t m1 = h2_dup(-(dm.y * (float)mn));
+    const uint32_t k1024 = 0x64006400u;
+    const int shift = half ? 4 : 0;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t word = u4_word(t.r[1 + 2 * kc + (i >> 4)], (i >> 2) & 3);
-      const uint32_t byte = (word >> (8 * (i & 3))) & 0xFF;
-      const float qv = (float)(half ? (byte >> 4) : (byte & 15));
-      v[i] = fmaf(d1, qv, -m1);
+    for (int i = 0; i < 8; ++i) {  // word i: bytes 4i .. 4i+3 of the sub-block pair -> elements 4i .. 4i+3
+      const uint32_t word = (u4_word(t.r[1 + 2 * kc + (i >> 2)], i & 3) >> shift) & 0x0F0F0F0Fu;
+      uint32_t lo, hi;
+      bytes_to_h2_biased(word, lo, hi);
+      out[2 * i] = h2_fma(h2_sub(lo, k1024), d1, m1);
+      out[2 * i + 1] = h2_fma(h2_sub(hi, k1024), d1, m1);
     }
   } else if (type == T_Q6_K) {
     const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
     const float d = half_bits_to_float((uint16_t)t.r[9].x);
     // sub-block scales 8hh + 2j and + 1 (signed bytes)
     const uint32_t sw = u4_word(t.r[8], 2 * hh + (j >> 1));
-    const float s0 = d * (float)(int)(int8_t)((sw >> (16 * (j & 1))) & 0xFF);
-    const float s1 = d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8)) & 0xFF);
+    const uint32_t s0 = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1))) & 0xFF));
+    const uint32_t s1 = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8)) & 0xFF));
+    const uint32_t k1056 = 0x64206420u;  // 1024 + 32: removes the bias and the format's offset of 32 at once
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t lword = u4_word(t.r[2 * hh + (i >> 4)], (i >> 2) & 3);
-      const uint32_t hword = u4_word(t.r[4 + 2 * hh + (i >> 4)], (i >> 2) & 3);
-      const uint32_t lbyte = (lword >> (8 * (i & 3))) & 0xFF, hbyte = (hword >> (8 * (i & 3))) & 0xFF;
-      const int nib = (j >> 1) ? (int)(lbyte >> 4) : (int)(lbyte & 15);
-      const int qv = (nib | (int)(((hbyte >> (2 * j)) & 3) << 4)) - 32;
-      v[i] = (i < 16 ? s0 : s1) * (float)qv;
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t lword = u4_word(t.r[2 * hh + (i >> 2)], i & 3);
+      const uint32_t hword = u4_word(t.r[4 + 2 * hh + (i >> 2)], i & 3);
+      const uint32_t nib = ((j >> 1) ? (lword >> 4) : lword) & 0x0F0F0F0Fu;
+      const uint32_t top = (j == 0 ? (hword << 4) : j == 1 ? (hword << 2) : j == 2 ? hword : (hword >> 2)) & 0x30303030u;
+      uint32_t lo, hi;
+      bytes_to_h2_biased(nib | top, lo, hi);
+      const uint32_t sc = i < 4 ? s0 : s1;
+      out[2 * i] = h2_mul(h2_sub(lo, k1056), sc);
+      out[2 * i + 1] = h2_mul(h2_sub(hi, k1056), sc);
     }
   } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
     const int b32 = 2 * kc + half;
     const uint32_t dwv = u4_word(t.r[8], b32 >> 1);
-    const float d = scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF));
+    const uint32_t d = h2_dup(scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF)));
+    const uint32_t k1152 = 0x64806480u;  // 1024 + 128
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t word = u4_word(t.r[2 * kc + (i >> 4)], (i >> 2) & 3);
-      v[i] = d * (float)(int)(int8_t)((word >> (8 * (i & 3))) & 0xFF);
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t word = u4_word(t.r[2 * kc + (i >> 2)], i & 3) ^ 0x80808080u;  // int8 + 128 as an unsigned byte
+      uint32_t lo, hi;
+      bytes_to_h2_biased(word, lo, hi);
+      out[2 * i] = h2_mul(h2_sub(lo, k1152), d);
+      out[2 * i + 1] = h2_mul(h2_sub(hi, k1152), d);
     }
   }
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
-    w[c] = make_uint4(pack_h2(v[8 * c], v[8 * c + 1]), pack_h2(v[8 * c + 2], v[8 * c + 3]), pack_h2(v[8 * c + 4], v[8 * c + 5]),
-                      pack_h2(v[8 * c + 6], v[8 * c + 7]));
+  for (int c = 0; c < 4; ++c) w[c] = make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
 }
 
 struct TcShared {
