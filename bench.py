@@ -145,6 +145,7 @@ def main():
         return run_reference(args, shape, scheme, batch, prompt_len)
 
     rank, local_rank, world = dist_env()
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
     warmup = max(args.warmup, 3)
     pkg = __graft_entry__.load_package()
     dist = None
