@@ -149,18 +149,31 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 }
 
 
+// cuTensorMapEncodeTiled, fetched from the driver at run time (the library links only the runtime).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (!p || q != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
 // Starts the tensor-core matmul for T tokens (gemm_tc.cuh). x16: [T][K] fp16 activations.
 static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   static bool attr_done = false;
   if (!attr_done) {
-    CK(cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(64)));
-    CK(cudaFuncSetAttribute(gemm_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
+    CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
     attr_done = true;
   }
   const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
   p.nblk = g0.nblk; p.nslab = g0.nslab; p.S = g0.S; p.S_last = g0.S_last; p.R = g0.R;
-  // token tile: the whole batch when it fits one tile, else 256 / 128 (two accumulator tiles of 256 columns fit TMEM, one is used)
-  int NT = (p.T + 15) / 16 * 16;
+  int NT = (p.T + 31) / 32 * 32;  // token tile: the whole batch when it fits, else tiles of 256
   if (NT > TC_MAX_N) NT = TC_MAX_N;
   p.NT = NT;
   p.tmem_cols = 32;
@@ -169,9 +182,18 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   for (int s = 0; s < p.nseg; ++s) p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
   p.error_flag = e->d_error;
   if (p.ksplit < 1) { p.ksplit = 1; p.kblocks = p.K / 256; }
+  // activation tiles: 64 elements along K x NT tokens, written in the 128-byte-swizzle layout; tokens beyond T read as zero
+  CUtensorMap tm;
+  const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+  const cuuint64_t gstr[1] = {(cuuint64_t)p.K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)NT};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = tensor_map_encoder()(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(p.x16), gdim, gstr, box, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
   dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT, p.ksplit);
-  if (NT <= 64) gemm_tc_kernel<2><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
-  else gemm_tc_kernel<8><<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p);
+  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p, tm);
   CK(cudaGetLastError());
 }
 

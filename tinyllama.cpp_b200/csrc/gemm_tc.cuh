@@ -21,14 +21,17 @@
 // so results agree with the FP32 reference dot to about 1e-3 of the largest output, not to 1e-3 of
 // each element; the parity tests state that tolerance.
 #pragma once
+#include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through cudaGetDriverEntryPoint)
+
 #include "gemv.cuh"
 
 namespace b200 {
 
 constexpr int TC_M = 128;        // weight rows per CTA tile (the MMA's M)
 constexpr int TC_KC = 64;        // elements along K per shared-memory stage: one 128-byte swizzled row of fp16
-constexpr int TC_THREADS = 256;
-constexpr int TC_MAX_N = 256;
+constexpr int TC_WORKERS = 512;   // sixteen dequantising warps: thread = (weight row, 16-element quarter of the 64-element step)
+constexpr int TC_THREADS = TC_WORKERS + 32;  // + one control warp
+constexpr int TC_MAX_N = 256;     // tokens per CTA tile
 
 struct TcParams {
   GemvSeg seg[3];
@@ -127,37 +130,33 @@ __device__ __forceinline__ TcUnit tc_locate(const TcParams& p, const GemvSeg& sg
   return u;
 }
 
-// The packed bytes of one 256-element block that one thread (row, half) needs for the block's four
-// K steps, fetched one block ahead of their use so that the loads overlap the previous block's
-// dequantisation and MMAs:
-//   Q4_K: r[0] = d, dmin, 12 scale bytes; r[1..8] = the 128 nibble bytes
-//   Q6_K: r[0..3] = ql[64h' + 32*half ..+32) for h' = 0, 1; r[4..7] = qh (64 bytes); r[8] = scales; r[9].x = d
-//   Q8_0: r[2kc .. 2kc+1] = quants of 32-block 2kc + half; r[8] = the eight fp16 d
+// The packed bytes of one 256-element block that one thread needs for the block's four K steps,
+// fetched one block ahead of their use so that the loads overlap the previous block's work. A
+// thread owns (row, half, sub): elements [64*kc + 32*half + 16*sub, +16) of every step kc.
+//   Q4_K: r[0] = d, dmin, 12 scale bytes; r[1 + kc] = its 16 nibble bytes of step kc
+//   Q6_K: r[hh] = its 16 ql bytes, r[2 + hh] = its 16 qh bytes of 128-element half hh; r[4] = scales; r[5].x = d
+//   Q8_0: r[kc] = its 16 quants of step kc; r[4] = the eight fp16 d
 struct TcRaw {
-  uint4 r[10];
+  uint4 r[6];
 };
 
-__device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, TcRaw& t) {
+__device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, int sub, TcRaw& t) {
   if (type == T_Q4_K) {
+    t.r[0] = __ldg(reinterpret_cast<const uint4*>(u.unit));
 #pragma unroll
-    for (int i = 0; i < 9; ++i) t.r[i] = __ldg(reinterpret_cast<const uint4*>(u.unit) + i);
+    for (int kc = 0; kc < 4; ++kc) t.r[1 + kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc + 16 * sub));
   } else if (type == T_Q6_K) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      t.r[2 * hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half));
-      t.r[2 * hh + 1] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half + 16));
+      t.r[hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half + 16 * sub));
+      t.r[2 + hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 128 + 32 * hh + 16 * sub));
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) t.r[4 + i] = __ldg(reinterpret_cast<const uint4*>(u.unit + 128) + i);
-    t.r[8] = __ldg(reinterpret_cast<const uint4*>(u.unit + 192));
-    t.r[9].x = __ldg(reinterpret_cast<const uint16_t*>(u.d));
+    t.r[4] = __ldg(reinterpret_cast<const uint4*>(u.unit + 192));
+    t.r[5].x = __ldg(reinterpret_cast<const uint16_t*>(u.d));
   } else {
 #pragma unroll
-    for (int kc = 0; kc < 4; ++kc) {
-      t.r[2 * kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half)));
-      t.r[2 * kc + 1] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half) + 16));
-    }
-    t.r[8] = __ldg(reinterpret_cast<const uint4*>(u.unit + 256));
+    for (int kc = 0; kc < 4; ++kc) t.r[kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half) + 16 * sub));
+    t.r[4] = __ldg(reinterpret_cast<const uint4*>(u.unit + 256));
   }
 }
 
@@ -183,14 +182,14 @@ __device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
 }
 __device__ __forceinline__ uint32_t h2_dup(float f) { return pack_h2(f, f); }
 
-// Dequantises 32 consecutive elements of a row: elements [64*kc + 32*half, +32) of the block held
-// in `t`, to fp16, into four 16-byte chunks w[0..3] (eight halves each). kc is a compile-time
+// Dequantises the thread's 16 elements of step kc (elements [64*kc + 32*half + 16*sub, +16) of the
+// block held in `t`) to fp16: two 16-byte chunks w[0..1] (eight halves each). kc is a compile-time
 // constant at every call site (the K steps of a block are unrolled). The integers go to fp16
 // through the 1024 + byte trick (exact), the scale and offset are applied in fp16 pairs: about
 // two instructions per element. Formulas: reference dequantize_q4_k_m / dequantize_q6_k /
 // dequantize_q8_0_block (quantization.cpp:171-266, 1047-1052); the matmul contract is a tolerance.
-__device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, int half, uint4 (&w)[4]) {
-  uint32_t out[16];  // 32 halves, in element order
+__device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, int half, int sub, uint4 (&w)[2]) {
+  uint32_t out[8];  // 16 halves, in element order
   if (type == T_Q4_K) {
     const uint4 h = t.r[0];
     const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
@@ -208,14 +207,13 @@ __device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, i
       sc = (q(sb + 4) & 0xF) | ((q(sb - 4) >> 6) << 4);
       mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
     }
-    const uint32_t d1 = h2_dup(dm.x * (float)sc);
     // (folding the 1024 bias into the offset would lose precision: 1024 * d1 dwarfs the result; it is subtracted first, exactly)
-    const uint32_t m1 = h2_dup(-(dm.y * (float)mn));
+    const uint32_t d1 = h2_dup(dm.x * (float)sc), m1 = h2_dup(-(dm.y * (float)mn));
     const uint32_t k1024 = 0x64006400u;
     const int shift = half ? 4 : 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // word i: bytes 4i .. 4i+3 of the sub-block pair -> elements 4i .. 4i+3
-      const uint32_t word = (u4_word(t.r[1 + 2 * kc + (i >> 2)], i & 3) >> shift) & 0x0F0F0F0Fu;
+    for (int i = 0; i < 4; ++i) {  // word i: its bytes 4i .. 4i+3 -> elements 4i .. 4i+3
+      const uint32_t word = (u4_word(t.r[1 + kc], i) >> shift) & 0x0F0F0F0Fu;
       uint32_t lo, hi;
       bytes_to_h2_biased(word, lo, hi);
       out[2 * i] = h2_fma(h2_sub(lo, k1024), d1, m1);
@@ -223,45 +221,47 @@ __device__ __forceinline__ void tc_dequant32(int type, const TcRaw& t, int kc, i
     }
   } else if (type == T_Q6_K) {
     const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
-    const float d = half_bits_to_float((uint16_t)t.r[9].x);
-    // sub-block scales 8hh + 2j and + 1 (signed bytes)
-    const uint32_t sw = u4_word(t.r[8], 2 * hh + (j >> 1));
-    const uint32_t s0 = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1))) & 0xFF));
-    const uint32_t s1 = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8)) & 0xFF));
+    const float d = half_bits_to_float((uint16_t)t.r[5].x);
+    // sub-block scale 8hh + 2j + sub (signed byte)
+    const uint32_t sw = u4_word(t.r[4], 2 * hh + (j >> 1));
+    const uint32_t sc = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8 * sub)) & 0xFF));
     const uint32_t k1056 = 0x64206420u;  // 1024 + 32: removes the bias and the format's offset of 32 at once
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t lword = u4_word(t.r[2 * hh + (i >> 2)], i & 3);
-      const uint32_t hword = u4_word(t.r[4 + 2 * hh + (i >> 2)], i & 3);
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lword = u4_word(t.r[hh], i), hword = u4_word(t.r[2 + hh], i);
       const uint32_t nib = ((j >> 1) ? (lword >> 4) : lword) & 0x0F0F0F0Fu;
       const uint32_t top = (j == 0 ? (hword << 4) : j == 1 ? (hword << 2) : j == 2 ? hword : (hword >> 2)) & 0x30303030u;
       uint32_t lo, hi;
       bytes_to_h2_biased(nib | top, lo, hi);
-      const uint32_t sc = i < 4 ? s0 : s1;
       out[2 * i] = h2_mul(h2_sub(lo, k1056), sc);
       out[2 * i + 1] = h2_mul(h2_sub(hi, k1056), sc);
     }
   } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
     const int b32 = 2 * kc + half;
-    const uint32_t dwv = u4_word(t.r[8], b32 >> 1);
+    const uint32_t dwv = u4_word(t.r[4], b32 >> 1);
     const uint32_t d = h2_dup(scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF)));
     const uint32_t k1152 = 0x64806480u;  // 1024 + 128
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t word = u4_word(t.r[2 * kc + (i >> 2)], i & 3) ^ 0x80808080u;  // int8 + 128 as an unsigned byte
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t word = u4_word(t.r[kc], i) ^ 0x80808080u;  // int8 + 128 as an unsigned byte
       uint32_t lo, hi;
       bytes_to_h2_biased(word, lo, hi);
       out[2 * i] = h2_mul(h2_sub(lo, k1152), d);
       out[2 * i + 1] = h2_mul(h2_sub(hi, k1152), d);
     }
   }
-#pragma unroll
-  for (int c = 0; c < 4; ++c) w[c] = make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+  w[0] = make_uint4(out[0], out[1], out[2], out[3]);
+  w[1] = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
+constexpr int TC_B_STAGES = 4;  // activation tiles in flight (TMA)
+constexpr int TC_A_STAGES = 4;  // weight-tile stages: one per K step of a 256-element block
+
 struct TcShared {
-  unsigned long long mma_bar[2];  // the MMAs that read stage s have completed
-  unsigned long long done_bar;    // all MMAs of the tile have completed
+  unsigned long long a_full[TC_A_STAGES];  // all dequantising threads have stored their part of the weight tile
+  unsigned long long b_full[TC_B_STAGES];  // the activation tile has landed (TMA transaction bytes)
+  unsigned long long mma_done[TC_A_STAGES];  // the MMAs that read weight stage i (and its activation stage) have completed
+  unsigned long long done_bar;             // all MMAs of the tile have completed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -270,28 +270,42 @@ __device__ __forceinline__ void tc_fail(const TcParams& p, TcShared* sh) {
   sh->abort_flag = 1;
   if (p.error_flag) *reinterpret_cast<volatile int*>(p.error_flag) = 1;
 }
+__device__ __forceinline__ void tc_wait(const TcParams& p, TcShared* sh, void* bar, uint32_t parity) {
+  if (!*(volatile int*)&sh->abort_flag && !mbar_wait(bar, parity)) tc_fail(p, sh);
+}
 
-// grid = (128-row tiles over all segments, token tiles of NT); 256 threads.
-// dynamic shared memory (1024-byte aligned): 2 x (A tile 16 KB + B tile NT x 128 bytes)
-__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT) { return 1024 + 2 * ((size_t)TC_M * 128 + (size_t)NT * 128); }
+// 2-D tiled TMA load of one activation tile (64 elements along K x NT tokens, 128-byte swizzle)
+__device__ __forceinline__ void tc_tma_load_2d(void* dst, const void* tmap, int c0, int c1, void* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
 
-// BMAX: 16-byte activation chunks a thread moves per step (2: token tiles up to 64, two CTAs per SM; 8: up to 256).
-template <int BMAX>
-__global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(const TcParams p) {
+// grid = (128-row tiles over all segments, token tiles of NT, K splits); 544 threads: warps 0-15
+// dequantise the weight tile (thread = row x 16-element quarter), warp 16 moves the activation tiles
+// with TMA and issues the MMAs. No block-wide barrier inside the K loop: the roles meet on mbarriers.
+// dynamic shared memory (1024-byte aligned): 4 weight stages of 16 KB + 4 activation stages of NT x 128 bytes
+__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT) { return 1024 + TC_A_STAGES * (size_t)TC_M * 128 + TC_B_STAGES * (size_t)NT * 128; }
+
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ uint8_t tc_smem_raw[];
   __shared__ TcShared sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
-  const size_t stage_bytes = (size_t)TC_M * 128 + (size_t)p.NT * 128;
-  // ---- which rows, which tokens ----
+  uint8_t* const Abase = smem;                                 // [4][128 rows][128 B]
+  uint8_t* const Bbase = smem + TC_A_STAGES * TC_M * 128;      // [4][NT rows][128 B]
+  const uint32_t b_stage_bytes = (uint32_t)p.NT * 128;
+  // ---- which rows, which tokens, which part of K ----
   int seg = 0, mt = blockIdx.x;
   while (seg + 1 < p.nseg && mt >= (p.seg[seg].rows + TC_M - 1) / TC_M) { mt -= (p.seg[seg].rows + TC_M - 1) / TC_M; ++seg; }
   const GemvSeg& sg = p.seg[seg];
   const int row0 = mt * TC_M;             // first image row of the tile within the segment
   const int t0 = blockIdx.y * p.NT;       // first token of the tile
+  const int blk0 = blockIdx.z * p.kblocks;
+  const int nblocks = min(p.K / 256 - blk0, p.kblocks), nsteps = 4 * nblocks;
   if (tid == 0) {
-    mbar_init(&sh.mma_bar[0], 1);
-    mbar_init(&sh.mma_bar[1], 1);
+    for (int i = 0; i < TC_A_STAGES; ++i) { mbar_init(&sh.a_full[i], TC_WORKERS); mbar_init(&sh.mma_done[i], 1); }
+    for (int i = 0; i < TC_B_STAGES; ++i) mbar_init(&sh.b_full[i], 1);
     mbar_init(&sh.done_bar, 1);
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -301,79 +315,70 @@ __global__ void __launch_bounds__(TC_THREADS, BMAX <= 2 ? 2 : 1) gemm_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = sh.tmem_base;
-  const uint32_t idesc = tc_idesc(p.NT);
 
-  const int my_row = tid & (TC_M - 1), my_half = tid >> 7;  // this thread dequantises 32 elements of one row per step
-  const int irow = min(row0 + my_row, sg.rows - 1);         // rows past the segment repeat the last one; their results are dropped
-  const int blk0 = blockIdx.z * p.kblocks;
-  const int nblocks = min(p.K / 256 - blk0, p.kblocks), nsteps = 4 * nblocks;  // this CTA's share of K
-  const int nb_chunks = p.NT * 8;
-  auto fetch_b = [&](int step, uint4 (&bv)[BMAX]) {
-#pragma unroll
-    for (int i = 0; i < BMAX; ++i) {
-      const int idx = tid + i * TC_THREADS;
-      bv[i] = make_uint4(0u, 0u, 0u, 0u);
-      if (idx < nb_chunks && t0 + (idx >> 3) < p.T)
-        bv[i] = __ldg(reinterpret_cast<const uint4*>(p.x16 + (size_t)(t0 + (idx >> 3)) * p.K + (size_t)(4 * blk0 + step) * TC_KC + 8 * (idx & 7)));
-    }
-  };
-  TcRaw cur, nxt;
-  tc_fetch(sg.type, tc_locate(p, sg, irow, blk0), my_half, cur);
-  uint4 bcur[BMAX], bnxt[BMAX];
-  fetch_b(0, bcur);
-#pragma unroll 1
-  for (int blk = 0; blk < nblocks; ++blk) {
-    if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk0 + blk + 1), my_half, nxt);  // lands while this block is worked on
-#pragma unroll
-    for (int kc = 0; kc < 4; ++kc) {
-      const int step = 4 * blk + kc;
-      const int buf = kc & 1;
-      uint8_t* A = smem + buf * stage_bytes;
-      uint8_t* B = A + TC_M * 128;
-      if (step + 1 < nsteps) fetch_b(step + 1, bnxt);
-      // the MMAs that read this stage two steps ago must be done before it is overwritten
-      if (step >= 2) {
-        if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.mma_bar[buf], ((step >> 1) - 1) & 1)) tc_fail(p, &sh);
-      }
-      {
-        uint4 w[4];
-        tc_dequant32(sg.type, cur, kc, my_half, w);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + c)) = w[c];
-      }
-#pragma unroll
-      for (int i = 0; i < BMAX; ++i) {
-        const int idx = tid + i * TC_THREADS;
-        if (idx < nb_chunks) *reinterpret_cast<uint4*>(B + tc_swz(idx >> 3, idx & 7)) = bcur[i];
-      }
-      // generic-proxy stores -> visible to the tensor core's (async proxy) reads
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
+  if (warp == TC_WORKERS / 32) {
+    // ---- control warp: one lane moves activation tiles and issues the MMAs ----
+    if (lane == 0) {
+      const uint32_t idesc = tc_idesc(p.NT);
+      auto load_b = [&](int s) {  // activation tile of step s into stage s % 4
+        void* bar = &sh.b_full[s % TC_B_STAGES];
+        mbar_expect_tx(bar, b_stage_bytes);
+        tc_tma_load_2d(Bbase + (size_t)(s % TC_B_STAGES) * b_stage_bytes, &tmap, (4 * blk0 + s) * TC_KC, t0, bar);
+      };
+      for (int s = 0; s < nsteps && s < TC_B_STAGES - 1; ++s) load_b(s);
+      for (int s = 0; s < nsteps; ++s) {
+        // stage (s + 3) % 4 was read by the MMAs of step s - 1: refill it three steps ahead once they are done
+        if (s + TC_B_STAGES - 1 < nsteps) {
+          if (s >= 1) tc_wait(p, &sh, &sh.mma_done[(s - 1) % TC_A_STAGES], (uint32_t)(((s - 1) / TC_A_STAGES) & 1));
+          load_b(s + TC_B_STAGES - 1);
+        }
+        tc_wait(p, &sh, &sh.a_full[s % TC_A_STAGES], (uint32_t)((s / TC_A_STAGES) & 1));
+        tc_wait(p, &sh, &sh.b_full[s % TC_B_STAGES], (uint32_t)((s / TC_B_STAGES) & 1));
         tc_fence_after();
-        const uint32_t a0 = smem_u32(A), b0 = smem_u32(B);
+        const uint32_t a0 = smem_u32(Abase + (size_t)(s % TC_A_STAGES) * TC_M * 128);
+        const uint32_t b0 = smem_u32(Bbase + (size_t)(s % TC_B_STAGES) * b_stage_bytes);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4)
-          tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (step | k4) ? 1u : 0u);
-        tc_commit(&sh.mma_bar[buf]);
-        if (step == nsteps - 1) tc_commit(&sh.done_bar);
+          tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (s | k4) ? 1u : 0u);
+        tc_commit(&sh.mma_done[s % TC_A_STAGES]);
+        if (s == nsteps - 1) tc_commit(&sh.done_bar);
       }
-#pragma unroll
-      for (int i = 0; i < BMAX; ++i) bcur[i] = bnxt[i];
     }
-    cur = nxt;
+    __syncwarp();
+  } else {
+    // ---- dequantising warps: thread = (weight row, 16-element quarter of the step) ----
+    const int my_row = tid & (TC_M - 1), my_half = (tid >> 8) & 1, my_sub = (tid >> 7) & 1;
+    const int irow = min(row0 + my_row, sg.rows - 1);  // rows past the segment repeat the last one; their results are dropped
+    TcRaw cur, nxt;
+    tc_fetch(sg.type, tc_locate(p, sg, irow, blk0), my_half, my_sub, cur);
+#pragma unroll 1
+    for (int blk = 0; blk < nblocks; ++blk) {
+      if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk0 + blk + 1), my_half, my_sub, nxt);  // lands while this block is worked on
+#pragma unroll
+      for (int kc = 0; kc < 4; ++kc) {
+        uint8_t* A = Abase + (size_t)kc * TC_M * 128;  // stage = step % 4 = kc
+        uint4 w[2];
+        tc_dequant16(sg.type, cur, kc, my_half, my_sub, w);
+        // the MMAs that read this stage four steps ago must be done before it is overwritten
+        if (blk >= 1) tc_wait(p, &sh, &sh.mma_done[kc], (uint32_t)((blk - 1) & 1));
+#pragma unroll
+        for (int c = 0; c < 2; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + my_sub * 2 + c)) = w[c];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core's reads
+        mbar_arrive(&sh.a_full[kc]);
+      }
+      cur = nxt;
+    }
   }
-  // ---- epilogue: warp w reads TMEM lanes 32*(w & 3) .. +31 (= weight rows), the two warp groups split the tokens ----
-  if (!*(volatile int*)&sh.abort_flag && !mbar_wait(&sh.done_bar, 0)) tc_fail(p, &sh);
+  // ---- epilogue: warp w reads TMEM lanes 32*(w & 3) .. +31 (= weight rows), the four warp groups split the tokens ----
+  if (warp < TC_WORKERS / 32) tc_wait(p, &sh, &sh.done_bar, 0u);
   tc_fence_after();
-  if (!*(volatile int*)&sh.abort_flag) {
+  if (warp < TC_WORKERS / 32 && !*(volatile int*)&sh.abort_flag) {
     const int r_in_tile = 32 * (warp & 3) + lane;
     const int row_img = row0 + r_in_tile;
     const bool row_ok = row_img < sg.rows;
-    const int ncol_half = p.NT / 2;
-    const int c_begin = (warp >> 2) * ncol_half;
-    for (int c0 = c_begin; c0 < c_begin + ncol_half; c0 += 8) {
+    const int ncol_q = p.NT / 4;  // the four warps that share a lane quarter split the tokens (NT is a multiple of 32)
+    const int c_begin = (warp >> 2) * ncol_q;
+    for (int c0 = c_begin; c0 < c_begin + ncol_q; c0 += 8) {
       float v[8];
       tc_ld8(tmem_d + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, v);
 #pragma unroll
