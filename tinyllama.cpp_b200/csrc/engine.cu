@@ -27,12 +27,29 @@ static T* dev_alloc(b200_engine* e, size_t n) {
   return static_cast<T*>(p);
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver at run time (the library links only the runtime).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (!p || q != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
 static void set_gemv_attrs() {
   static bool done = false;
   if (done) return;
   const int maxb = GEMV_SMEM_BUDGET;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
+  CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
+  (void)tensor_map_encoder();
   CK(cudaFuncSetAttribute((attn_decode_kernel<true, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute((attn_decode_kernel<false, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute((attn_decode_kernel<true, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -149,28 +166,9 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 }
 
 
-// cuTensorMapEncodeTiled, fetched from the driver at run time (the library links only the runtime).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn tensor_map_encoder() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
-    if (!p || q != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
-    fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
 // Starts the tensor-core matmul for T tokens (gemm_tc.cuh). x16: [T][K] fp16 activations.
 static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
-    attr_done = true;
-  }
+  set_gemv_attrs();
   const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
   p.nblk = g0.nblk; p.nslab = g0.nslab; p.S = g0.S; p.S_last = g0.S_last; p.R = g0.R;
   int NT = (p.T + 31) / 32 * 32;  // token tile: the whole batch when it fits, else tiles of 256
@@ -299,7 +297,7 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
     return 1;
   }
   __half* x16 = static_cast<__half*>(x16_buf ? x16_buf : e->d_x16);
-  to_half_kernel<<<batch, 256, 0, st>>>(p.x, p.x_stride, p.norm_w, p.eps, p.K, x16);
+  to_half_kernel<<<batch, TOH_THREADS, 0, st>>>(p.x, p.x_stride, p.norm_w, p.eps, p.K, x16);
   CK(cudaGetLastError());
   TcParams t{};
   for (int s = 0; s < p.nseg; ++s) t.seg[s] = p.seg[s];
@@ -311,9 +309,8 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
   const int ctas = (int)((p.seg[0].rows + TC_M - 1) / TC_M) * ((batch + TC_MAX_N - 1) / TC_MAX_N);
   const int nblk = p.K / 256;
   int ks = 1;
-  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 256) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
+  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 256 && e->d_tc_part) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
   if (ks > 1) {
-    if (!e->d_tc_part) e->d_tc_part = dev_alloc<float>(e, (size_t)8 * 256 * e->H);
     t.ksplit = ks; t.kblocks = (nblk + ks - 1) / ks;
     t.ksplit = (nblk + t.kblocks - 1) / t.kblocks;  // no empty split
     t.epi = EPI_STORE; t.y = e->d_tc_part; t.y_stride = p.seg[0].rows;

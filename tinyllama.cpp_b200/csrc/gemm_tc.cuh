@@ -258,7 +258,7 @@ constexpr int TC_B_STAGES = 4;  // activation tiles in flight (TMA)
 constexpr int TC_A_STAGES = 4;  // weight-tile stages: one per K step of a 256-element block
 
 struct TcShared {
-  unsigned long long a_full[TC_A_STAGES];  // all dequantising threads have stored their part of the weight tile
+  unsigned long long a_full[TC_A_STAGES];  // all dequantising warps have stored their part of the weight tile
   unsigned long long b_full[TC_B_STAGES];  // the activation tile has landed (TMA transaction bytes)
   unsigned long long mma_done[TC_A_STAGES];  // the MMAs that read weight stage i (and its activation stage) have completed
   unsigned long long done_bar;             // all MMAs of the tile have completed
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
   const int blk0 = blockIdx.z * p.kblocks;
   const int nblocks = min(p.K / 256 - blk0, p.kblocks), nsteps = 4 * nblocks;
   if (tid == 0) {
-    for (int i = 0; i < TC_A_STAGES; ++i) { mbar_init(&sh.a_full[i], TC_WORKERS); mbar_init(&sh.mma_done[i], 1); }
+    for (int i = 0; i < TC_A_STAGES; ++i) { mbar_init(&sh.a_full[i], TC_WORKERS / 32); mbar_init(&sh.mma_done[i], 1); }
     for (int i = 0; i < TC_B_STAGES; ++i) mbar_init(&sh.b_full[i], 1);
     mbar_init(&sh.done_bar, 1);
     sh.abort_flag = 0;
@@ -364,7 +364,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 #pragma unroll
         for (int c = 0; c < 2; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + my_sub * 2 + c)) = w[c];
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core's reads
-        mbar_arrive(&sh.a_full[kc]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.a_full[kc]);  // one arrival per warp: 512 arrivals on one barrier word would serialise
       }
       cur = nxt;
     }
@@ -440,28 +441,56 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int ksplit,
 }
 
 // x16[t][k] = fp16(x[t][k]) or, with norm weights, fp16(RMSNorm(x[t])[k]) (reference rmsnorm_batch_cpu,
-// utils.cpp:613-646: f = 1/sqrtf(mean(x^2) + eps), out = x * f * w). One block per token.
-__global__ void to_half_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ norm_w, float eps, int K,
-                               __half* __restrict__ out) {
-  __shared__ float red[33];
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const float* xr = x + (size_t)t * x_stride;
+// utils.cpp:613-646: f = 1/sqrtf(mean(x^2) + eps), out = x * f * w). One block of 512 threads per token;
+// the row stays in registers between the two passes (rows of up to 16384 elements, else it is read again).
+constexpr int TOH_THREADS = 512;
+__global__ void __launch_bounds__(TOH_THREADS) to_half_kernel(const float* __restrict__ x, int x_stride, const float* __restrict__ norm_w, float eps, int K,
+                                                              __half* __restrict__ out) {
+  __shared__ float red[TOH_THREADS / 32 + 1];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)t * x_stride);
+  const int n4 = K / 4;  // K is a multiple of 256
+  constexpr int KEEP = 8;
+  float4 v[KEEP];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int j = tid + i * TOH_THREADS;
+    v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  for (int j = tid + KEEP * TOH_THREADS; j < n4; j += TOH_THREADS) {
+    const float4 a = xr[j];
+    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
   float f = 1.0f;
   if (norm_w) {
-    float ss = 0.f;
-    for (int i = tid; i < K; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
     __syncthreads();
     if (tid == 0) {
       float tot = 0.f;
-      for (int w = 0; w < nwarps; ++w) tot += red[w];
-      red[32] = 1.0f / sqrtf(tot / (float)K + eps);
+      for (int w = 0; w < TOH_THREADS / 32; ++w) tot += red[w];
+      red[TOH_THREADS / 32] = 1.0f / sqrtf(tot / (float)K + eps);
     }
     __syncthreads();
-    f = red[32];
+    f = red[TOH_THREADS / 32];
   }
-  for (int i = tid; i < K; i += blockDim.x) out[(size_t)t * K + i] = __float2half_rn(norm_w ? xr[i] * f * norm_w[i] : xr[i]);
+  const float4* wr = reinterpret_cast<const float4*>(norm_w);
+  uint2* orow = reinterpret_cast<uint2*>(out + (size_t)t * K);
+  auto emit = [&](int j, float4 a) {
+    if (norm_w) {
+      const float4 w = __ldg(wr + j);
+      a.x = a.x * f * w.x; a.y = a.y * f * w.y; a.z = a.z * f * w.z; a.w = a.w * f * w.w;
+    }
+    orow[j] = make_uint2(pack_h2(a.x, a.y), pack_h2(a.z, a.w));
+  };
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int j = tid + i * TOH_THREADS;
+    if (j < n4) emit(j, v[i]);
+  }
+  for (int j = tid + KEEP * TOH_THREADS; j < n4; j += TOH_THREADS) emit(j, xr[j]);
 }
 
 }  // namespace b200
