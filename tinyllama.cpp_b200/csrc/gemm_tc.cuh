@@ -4,18 +4,21 @@
 // (model.cpp:2141-2249). "Swap-AB": the weight rows are the M side of the MMA (128 per CTA tile),
 // the tokens the N side (16..256 per tile).
 //
-// Per 64-element step along K the CTA's 256 threads
-//   * read the packed units of their weight row straight from the stage images, dequantise 32
-//     elements each to fp16 and store them into the A tile (128 rows x 128 bytes) in the K-major
+// A CTA (544 threads) owns one tile of 128 rows x NT tokens and walks K in steps of 64 elements.
+// Three roles meet only on mbarriers; there is no block-wide barrier inside the K loop:
+//   * sixteen warps dequantise: a thread owns (row, 16-element quarter of the step), fetches its
+//     packed bytes one 256-element block ahead, straight from the stage images, converts them to
+//     fp16 and stores them into one of four weight stages (128 rows x 128 bytes) in the K-major
 //     128-byte-swizzle layout the MMA unit reads from shared memory;
-//   * copy the matching slice of the fp16 activations into the B tile (N rows x 128 bytes, same layout);
-// then one thread issues four tcgen05.mma (M=128, N, K=16, kind::f16) that accumulate into a
-// 128-lane x N-column fp32 tile in tensor memory and commits them to an mbarrier. Two A/B stages
-// alternate, so the dequantisation of step i+1 overlaps the MMAs of step i. After the last step
-// the warps read their TMEM lanes back (tcgen05.ld 32x32b: thread = weight row, registers =
-// tokens) and run the same epilogues as the matvec kernel (store, residual add, RoPE scatter,
-// SwiGLU). Every wait is bounded; on a give-up the kernel sets the error word, frees its tensor
-// memory and returns.
+//   * one lane of the control warp moves the matching slices of the fp16 activations with TMA
+//     (cp.async.bulk.tensor.2d, same swizzle, tokens beyond T read as zero) into four activation
+//     stages, three steps ahead, and issues four tcgen05.mma (M=128, N=NT, K=16, kind::f16) per
+//     step that accumulate into a 128-lane x NT-column fp32 tile in tensor memory; tcgen05.commit
+//     tells the dequantising warps when a stage may be overwritten;
+//   * after the last step the sixteen warps read their TMEM lanes back (tcgen05.ld 32x32b:
+//     thread = weight row, registers = tokens) and run the same epilogues as the matvec kernel
+//     (store, residual add, RoPE scatter, SwiGLU).
+// Every wait is bounded; on a give-up the kernel sets the error word, frees its tensor memory and returns.
 //
 // fp16 operands: dequantised weights are rounded to fp16 (relative 2^-11) and activations likewise,
 // so results agree with the FP32 reference dot to about 1e-3 of the largest output, not to 1e-3 of
