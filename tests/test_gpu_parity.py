@@ -348,3 +348,48 @@ def test_step_trace_records(pkg, tiny_models, monkeypatch):
         plain.read_trace()
     plain.close()
     eng.close()
+
+
+@pytest.mark.parametrize("name,rows,cols", [("q4_k", 48, 8192), ("q6_k", 40, 14336), ("q4_k", 33, 28672), ("q6_k", 18, 28672),
+                                            ("q8_0", 20, 8192)])
+def test_matvec_long_rows_of_the_8b_and_70b_shapes(pkg, name, rows, cols):
+    """Input widths of the 8B / 70B shapes: 32, 56 and 112 blocks per row (2, 4 and 7 stages per tile)."""
+    typ = TYPES[name]
+    w = pkg.synth.fill_normal(rows * cols, 31, rows + typ, 0.02)
+    blocks = pkg.synth.quantize(typ, w)
+    x = pkg.synth.fill_normal(cols, 32, cols, 1.0)
+    wd = ol.dequant("oracle", typ, blocks).reshape(rows, cols)
+    ref = ol.matvec_f32("oracle", wd, x)
+    y = pkg.api.matvec(typ, blocks, rows, cols, x)
+    assert rel_err(y, ref) <= 1e-3
+    xs = pkg.synth.fill_normal(32 * cols, 33, cols, 1.0).reshape(32, cols)
+    ref2 = (wd.astype(np.float64) @ xs.astype(np.float64).T).T
+    y2 = pkg.api.matmul(typ, blocks, rows, cols, xs)
+    assert np.abs(y2 - ref2).max() <= 2e-3 * np.abs(ref2).max()
+
+
+@pytest.mark.parametrize("kv", ["f32", "i8"])
+@pytest.mark.parametrize("shape,scheme", [("llama3-8b", 2), ("llama2-70b", 1)])
+def test_two_layer_models_of_the_large_shapes(pkg, tmp_path, shape, scheme, kv):
+    """Two layers of the 8B (GQA 32/8, FFN 14336, all Q6_K) and 70B (GQA 64/8, hidden 8192, FFN 28672, Q4_K_M-style)
+    shapes with a small vocabulary: decode steps (matvec path) and a 20-token prompt (tensor-core path) against the
+    oracle. With an INT8 cache the prompt tolerance is relative: fp16-level differences in K/V flip the rounding of
+    some cached int8 values by one step, which moves the logits by about as much as the cache quantisation itself
+    (measured 0.7 % of the largest logit; with an FP32 cache the same path stays below 2e-2 absolute)."""
+    path = pkg.synth.write_gguf(str(tmp_path / "m.gguf"), shape, scheme=scheme, n_layers=2, vocab=4096, max_pos=256)
+    i8 = kv == "i8"
+    eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if i8 else pkg.KV_F32, max_seqs=2, max_ctx=64)
+    orc = ol.OracleModel.from_gguf(path, kv_int8=i8, max_seqs=2)
+    tok = 11
+    for pos in range(3):
+        logits, amax = eng.decode([tok], [pos])
+        ref = orc.decode(tok, pos, seq=0)
+        assert np.abs(logits[0] - ref).max() <= 2e-2
+        assert int(amax[0]) == int(ref.argmax())
+        tok = int(ref.argmax())
+    ids = (np.arange(20, dtype=np.int32) * 37 + 5) % 4096
+    got = eng.prefill(ids, slot=1)          # 20 tokens: the tensor-core path
+    ref = orc.prefill(ids, seq=1)
+    tol = 1.5e-2 * float(np.abs(ref).max()) if i8 else 2e-2
+    assert np.abs(got - ref).max() <= tol
+    eng.close()

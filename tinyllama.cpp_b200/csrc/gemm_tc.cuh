@@ -165,34 +165,21 @@ __device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, in
 
 __device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-// Four bytes of `v` (values 0..255) as four fp16 numbers 1024 + byte, two per word: 0x6400 is
-// 1024.0 and an integer below 1024 in the low mantissa bits adds exactly. lo = bytes 0, 1; hi = bytes 2, 3.
-__device__ __forceinline__ void bytes_to_h2_biased(uint32_t v, uint32_t& lo, uint32_t& hi) {
-  lo = __byte_perm(v, 0x64646464u, 0x4140);  // [b0, 0x64, b1, 0x64]
-  hi = __byte_perm(v, 0x64646464u, 0x4342);  // [b2, 0x64, b3, 0x64]
+// Byte k of `v` (0..255) as a float, without an integer-to-float conversion: 0x4B0000bb is
+// 8388608 + bb, and subtracting 8388608 (+ the format's own offset) is exact.
+__device__ __forceinline__ float byte_to_float(uint32_t v, int k, float bias) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 | k)) - bias;
 }
-__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
-  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b), *reinterpret_cast<const __half2*>(&c));
-  return *reinterpret_cast<const uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
-  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
-  return *reinterpret_cast<const uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
-  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
-  return *reinterpret_cast<const uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t h2_dup(float f) { return pack_h2(f, f); }
 
 // Dequantises the thread's 16 elements of step kc (elements [64*kc + 32*half + 16*sub, +16) of the
 // block held in `t`) to fp16: two 16-byte chunks w[0..1] (eight halves each). kc is a compile-time
-// constant at every call site (the K steps of a block are unrolled). The integers go to fp16
-// through the 1024 + byte trick (exact), the scale and offset are applied in fp16 pairs: about
-// two instructions per element. Formulas: reference dequantize_q4_k_m / dequantize_q6_k /
+// constant at every call site (the K steps of a block are unrolled). Each weight is computed in
+// FP32 as the reference does and rounded to fp16 once (scaling in fp16 pairs was measured to triple
+// the error of the products: the sub-block scale's rounding is shared by 16 or 32 weights and does
+// not average out). Formulas: reference dequantize_q4_k_m / dequantize_q6_k /
 // dequantize_q8_0_block (quantization.cpp:171-266, 1047-1052); the matmul contract is a tolerance.
 __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, int half, int sub, uint4 (&w)[2]) {
-  uint32_t out[8];  // 16 halves, in element order
+  float v[16];
   if (type == T_Q4_K) {
     const uint4 h = t.r[0];
     const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
@@ -210,51 +197,42 @@ __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, i
       sc = (q(sb + 4) & 0xF) | ((q(sb - 4) >> 6) << 4);
       mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
     }
-    // (folding the 1024 bias into the offset would lose precision: 1024 * d1 dwarfs the result; it is subtracted first, exactly)
-    const uint32_t d1 = h2_dup(dm.x * (float)sc), m1 = h2_dup(-(dm.y * (float)mn));
-    const uint32_t k1024 = 0x64006400u;
+    const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
     const int shift = half ? 4 : 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // word i: its bytes 4i .. 4i+3 -> elements 4i .. 4i+3
       const uint32_t word = (u4_word(t.r[1 + kc], i) >> shift) & 0x0F0F0F0Fu;
-      uint32_t lo, hi;
-      bytes_to_h2_biased(word, lo, hi);
-      out[2 * i] = h2_fma(h2_sub(lo, k1024), d1, m1);
-      out[2 * i + 1] = h2_fma(h2_sub(hi, k1024), d1, m1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[4 * i + k] = fmaf(d1, byte_to_float(word, k, 8388608.0f), -m1);
     }
   } else if (type == T_Q6_K) {
     const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
     const float d = half_bits_to_float((uint16_t)t.r[5].x);
     // sub-block scale 8hh + 2j + sub (signed byte)
     const uint32_t sw = u4_word(t.r[4], 2 * hh + (j >> 1));
-    const uint32_t sc = h2_dup(d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8 * sub)) & 0xFF));
-    const uint32_t k1056 = 0x64206420u;  // 1024 + 32: removes the bias and the format's offset of 32 at once
+    const float sc = d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8 * sub)) & 0xFF);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t lword = u4_word(t.r[hh], i), hword = u4_word(t.r[2 + hh], i);
       const uint32_t nib = ((j >> 1) ? (lword >> 4) : lword) & 0x0F0F0F0Fu;
       const uint32_t top = (j == 0 ? (hword << 4) : j == 1 ? (hword << 2) : j == 2 ? hword : (hword >> 2)) & 0x30303030u;
-      uint32_t lo, hi;
-      bytes_to_h2_biased(nib | top, lo, hi);
-      out[2 * i] = h2_mul(h2_sub(lo, k1056), sc);
-      out[2 * i + 1] = h2_mul(h2_sub(hi, k1056), sc);
+      const uint32_t six = nib | top;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[4 * i + k] = sc * byte_to_float(six, k, 8388640.0f);  // removes the format's offset of 32 as well
     }
   } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
     const int b32 = 2 * kc + half;
     const uint32_t dwv = u4_word(t.r[4], b32 >> 1);
-    const uint32_t d = h2_dup(scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF)));
-    const uint32_t k1152 = 0x64806480u;  // 1024 + 128
+    const float d = scale_field_to_float((uint16_t)((dwv >> (16 * (b32 & 1))) & 0xFFFF));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t word = u4_word(t.r[kc], i) ^ 0x80808080u;  // int8 + 128 as an unsigned byte
-      uint32_t lo, hi;
-      bytes_to_h2_biased(word, lo, hi);
-      out[2 * i] = h2_mul(h2_sub(lo, k1152), d);
-      out[2 * i + 1] = h2_mul(h2_sub(hi, k1152), d);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[4 * i + k] = d * byte_to_float(word, k, 8388736.0f);  // 8388608 + 128
     }
   }
-  w[0] = make_uint4(out[0], out[1], out[2], out[3]);
-  w[1] = make_uint4(out[4], out[5], out[6], out[7]);
+  w[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+  w[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
 }
 
 constexpr int TC_B_STAGES = 4;  // activation tiles in flight (TMA)
