@@ -1,4 +1,4 @@
-"""Tensor-parallel engines (one process per GPU, NCCL all-reduce) against the CPU oracle.
+"""Tensor-parallel engines (one process per GPU; one-shot all-reduce over peer memory, or NCCL) against the CPU oracle.
 Needs two GPUs; skipped otherwise."""
 import numpy as np
 import pytest
@@ -6,7 +6,9 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _rank(rank, world, path, id_q, out_q, kv_i8):
+def _rank(rank, world, path, id_q, out_q, kv_i8, fused):
+    import os
+    os.environ["B200_TP_FUSED"] = "1" if fused else "0"  # peer-memory exchange inside the matvec kernels, or ncclAllReduce
     import __graft_entry__
     pkg = __graft_entry__.load_package()
     if rank == 0:
@@ -30,8 +32,9 @@ def _rank(rank, world, path, id_q, out_q, kv_i8):
     eng.close()
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("kv_i8", [False, True])
-def test_tp2_matches_oracle(pkg, tmp_path, kv_i8):
+def test_tp2_matches_oracle(pkg, tmp_path, kv_i8, fused):
     if pkg.api.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -39,7 +42,7 @@ def test_tp2_matches_oracle(pkg, tmp_path, kv_i8):
     path = pkg.synth.write_gguf(str(tmp_path / "mha.gguf"), "tiny_mha", scheme=1, norm_random=True)
     ctx = mp.get_context("spawn")
     id_q, out_q = ctx.Queue(), ctx.Queue()
-    procs = [ctx.Process(target=_rank, args=(r, 2, path, id_q, out_q, kv_i8)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, path, id_q, out_q, kv_i8, fused)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted((out_q.get(timeout=300) for _ in procs), key=lambda t: t[0])
