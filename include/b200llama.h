@@ -126,6 +126,14 @@ int b200_attention_decode(const float* q, const float* k_new, const float* v_new
                           const float* v_cache, int n_ctx, int n_heads, int n_kv_heads, int head_dim,
                           int kv_dtype, int n_splits, float* out);
 
+/* Causal attention of the last n_tokens positions of one sequence of n_ctx positions: the prompt form
+ * (attention_batch_cpu, cpu_attention.cpp:91-201; attention_batch_prefill_cuda, cuda_kernels.cu:1710, 2055).
+ * q [n_tokens][n_heads][hd] (rotated); k_rows, v_rows [n_ctx][n_kv][hd] FP32, rows of the n_tokens
+ * included (quantized on upload when kv_dtype is I8); out [n_tokens][n_heads][hd]. head_dim 64 or 128.
+ * fp16 tensor-core products with FP32 accumulation: agrees with the FP32 form to about 1e-3. */
+int b200_attention_prefill(const float* q, const float* k_rows, const float* v_rows, int n_ctx, int n_tokens,
+                           int n_heads, int n_kv_heads, int head_dim, int kv_dtype, float* out);
+
 /* No counterpart in the reference. Decode attention for callers that must not allocate device
  * memory at the moment of the call (stream capture in progress, memory handed out once by an
  * external pool, allocator frozen after start-up). All pointers are DEVICE pointers owned by the

@@ -141,6 +141,30 @@ def test_attention_decode(pkg, kv_i8, nq, nkv, hd, n_ctx, splits):
     assert np.abs(out - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("kv_i8", [False, True])
+@pytest.mark.parametrize("nq,nkv,hd,n_ctx,n_tok", [(4, 2, 64, 40, 40), (4, 4, 64, 130, 1), (8, 2, 128, 333, 77),
+                                                  (32, 8, 128, 1100, 256), (2, 1, 128, 64, 64), (2, 2, 64, 65, 65)])
+def test_attention_prefill(pkg, kv_i8, nq, nkv, hd, n_ctx, n_tok):
+    """Prompt attention on the fp16 tensor cores against the per-token FP32 attention of the oracle
+    (each token attends to the rows up to its own position). Tolerance 3e-3 of the largest output:
+    Q, FP32 K / V rows and the probabilities are rounded to fp16 (2^-11 relative each)."""
+    rng = np.random.default_rng(n_ctx * 7 + nq)
+    q = rng.standard_normal((n_tok, nq * hd)).astype(np.float32)
+    kc = rng.standard_normal((n_ctx, nkv, hd)).astype(np.float32)
+    vc = rng.standard_normal((n_ctx, nkv, hd)).astype(np.float32)
+    if n_ctx > 2:
+        kc[1] = 0.0
+        vc[2] = 0.0  # all-zero rows: INT8 scale falls back to 1.0
+    start = n_ctx - n_tok
+    out = pkg.api.attention_prefill(q, kc, vc, nq, nkv, hd, kv_dtype=pkg.KV_I8 if kv_i8 else pkg.KV_F32)
+    worst, big = 0.0, 1.0
+    for i in range(n_tok):
+        ref = ol.attention_decode(q[i], kc[:start + i + 1], vc[:start + i + 1], nq, nkv, hd, kv_int8=kv_i8)
+        worst = max(worst, float(np.abs(out[i] - ref).max()))
+        big = max(big, float(np.abs(ref).max()))
+    assert worst <= 3e-3 * big, (worst, big)
+
+
 def run_greedy(eng, orc, first, steps, start=0):
     tok, ids_e, ids_o, worst, margins = first, [], [], 0.0, []
     for pos in range(start, start + steps):

@@ -29,7 +29,7 @@ EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
-    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_attention_decode",
+    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
     "b200_nccl_unique_id", "b200_tp_share"]
 
@@ -64,6 +64,7 @@ def lib():
     L.b200_matvec.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _i, _vp]
     L.b200_rmsnorm.argtypes = [_vp, _vp, _i, ctypes.c_float, _vp]
     L.b200_attention_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
+    L.b200_attention_prefill.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
     L.b200_attention_decode_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
     L.b200_engine_stats.argtypes = [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.b200_engine_time_kernel.argtypes = [_vp, _i, _i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_i64)]
@@ -243,6 +244,17 @@ def attention_decode(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv_heads, hea
     out = np.empty(n_heads * head_dim, np.float32)
     _check(lib().b200_attention_decode(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), n_ctx, n_heads,
                                        n_kv_heads, head_dim, kv_dtype, n_splits, _ptr(out)))
+    return out
+
+
+def attention_prefill(q, k_rows, v_rows, n_heads, n_kv_heads, head_dim, kv_dtype=KV_F32):
+    """Causal attention of the last len(q) positions over all rows of k_rows / v_rows (prompt form)."""
+    q, k_rows, v_rows = _f32(q), _f32(k_rows), _f32(v_rows)
+    n_tokens = q.size // (n_heads * head_dim)
+    n_ctx = k_rows.size // (n_kv_heads * head_dim)
+    out = np.empty((n_tokens, n_heads * head_dim), np.float32)
+    _check(lib().b200_attention_prefill(_ptr(q), _ptr(k_rows), _ptr(v_rows), n_ctx, n_tokens, n_heads, n_kv_heads, head_dim,
+                                        kv_dtype, _ptr(out)))
     return out
 
 

@@ -8,6 +8,7 @@
 
 #include "attn.cuh"
 #include "attn_cluster.cuh"
+#include "attn_prefill.cuh"
 #include "dequant.cuh"
 #include "gemv.cuh"
 #include "gemm_tc.cuh"
@@ -56,7 +57,33 @@ static void set_gemv_attrs() {
   CK(cudaFuncSetAttribute((attn_decode_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute((attn_decode_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute((attn_decode_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  CK(cudaFuncSetAttribute((attn_prefill_kernel<true, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 64)));
+  CK(cudaFuncSetAttribute((attn_prefill_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 128)));
+  CK(cudaFuncSetAttribute((attn_prefill_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 64)));
+  CK(cudaFuncSetAttribute((attn_prefill_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 128)));
   done = true;
+}
+
+// Prompt attention on the tensor cores handles head sizes 64 and 128; B200_PREFILL_ATTN=0 sends
+// prompts through the per-token decode kernel instead.
+static bool prefill_attn_available(int hd) {
+  static const bool on = [] { const char* v = std::getenv("B200_PREFILL_ATTN"); return !(v && v[0] == '0'); }();
+  return on && (hd == 64 || hd == 128);
+}
+
+static void launch_prefill_attention(const PrefillAttnParams& a, bool kv_i8, int hd, cudaStream_t st) {
+  const dim3 grid((a.T + PFA_Q - 1) / PFA_Q, a.nq);
+  const size_t smem = pfa_smem_bytes(kv_i8, hd);
+  if (hd == 128) {
+    if (kv_i8) attn_prefill_kernel<true, 128><<<grid, PFA_THREADS, smem, st>>>(a);
+    else attn_prefill_kernel<false, 128><<<grid, PFA_THREADS, smem, st>>>(a);
+  } else if (hd == 64) {
+    if (kv_i8) attn_prefill_kernel<true, 64><<<grid, PFA_THREADS, smem, st>>>(a);
+    else attn_prefill_kernel<false, 64><<<grid, PFA_THREADS, smem, st>>>(a);
+  } else {
+    throw std::runtime_error("prompt attention kernel: head_dim must be 64 or 128");
+  }
+  CK(cudaGetLastError());
 }
 
 // Uploads one packed tensor and lays it out on the device as the stage images the matvec kernel
@@ -522,7 +549,14 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
     kv_append_kernel<<<dim3(T, e->nkv, 2), 32, 0, st>>>(e->pf_kvnew, 2 * KVD, d_pos, d_slot, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0, w.k_cache,
                                                         w.v_cache, w.k_scale, w.v_scale);
     CK(cudaGetLastError());
-    {
+    if (prefill_attn_available(e->hd)) {
+      PrefillAttnParams a{};
+      a.q = e->pf_q; a.q_stride = e->Hq;
+      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+      a.slot = slot; a.start = start; a.T = T; a.nq = e->nq; a.nkv = e->nkv; a.max_ctx = e->max_ctx;
+      a.out = e->pf_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      launch_prefill_attention(a, i8, e->hd, st);
+    } else {
       AttnParams a{};
       a.q = e->pf_q; a.kv_new = e->pf_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
       a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
