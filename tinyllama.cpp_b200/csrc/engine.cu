@@ -49,7 +49,7 @@ static void set_gemv_attrs() {
   const int maxb = GEMV_SMEM_BUDGET;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
-  CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(TC_MAX_N)));
+  CK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_MAX));
   (void)tensor_map_encoder();
   CK(cudaFuncSetAttribute((attn_decode_kernel<true, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
   CK(cudaFuncSetAttribute((attn_decode_kernel<false, 0>), cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -194,6 +194,14 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
 
 
 // Starts the tensor-core matmul for T tokens (gemm_tc.cuh). x16: [T][K] fp16 activations.
+static void encode_map(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* gdim, const cuuint64_t* gstr,
+                       const cuuint32_t* box, CUtensorMapSwizzle swz) {
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult rc = tensor_map_encoder()(tm, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+}
+
 static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   set_gemv_attrs();
   const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
@@ -204,21 +212,54 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   p.tmem_cols = 32;
   while (p.tmem_cols < NT) p.tmem_cols *= 2;
   p.ntiles_m = 0;
-  for (int s = 0; s < p.nseg; ++s) p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
+  int ub_max = 0;
+  for (int s = 0; s < p.nseg; ++s) {
+    p.ntiles_m += (p.seg[s].rows + TC_M - 1) / TC_M;
+    ub_max = std::max(ub_max, gemv_unit_bytes(p.seg[s].type));
+  }
   p.error_flag = e->d_error;
   if (p.ksplit < 1) { p.ksplit = 1; p.kblocks = p.K / 256; }
-  // activation tiles: 64 elements along K x NT tokens, written in the 128-byte-swizzle layout; tokens beyond T read as zero
-  CUtensorMap tm;
-  const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
-  const cuuint64_t gstr[1] = {(cuuint64_t)p.K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)NT};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult rc = tensor_map_encoder()(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(p.x16), gdim, gstr, box, estr,
-                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+  // shared memory: a weight-tile ring two blocks deep when the token tile is narrow enough, fewer
+  // activation stages for the widest token tiles, the rest for the packed-weight ring
+  p.w_stage_bytes = (TC_M * ub_max + 127) / 128 * 128;
+  static const int a_force = [] { const char* v = std::getenv("B200_TC_A_STAGES"); return v ? atoi(v) : 0; }();
+  p.a_stages = NT <= 128 ? 8 : 4;
+  if (a_force == 4 || a_force == 8) p.a_stages = a_force;
+  p.b_stages = NT > 128 ? 3 : 4;
+  auto fits = [&](int w) { return tc_smem_bytes(NT, p.a_stages, p.b_stages, w, p.w_stage_bytes) <= (size_t)TC_SMEM_MAX; };
+  if (p.a_stages == 8 && !fits(2)) { p.b_stages = 2; if (!fits(1)) { p.a_stages = 4; p.b_stages = NT > 128 ? 3 : 4; } }
+  p.w_stages = TC_W_STAGES;
+  while (p.w_stages > 1 && !fits(p.w_stages)) --p.w_stages;
+  if (!fits(p.w_stages)) throw std::runtime_error("tensor-core matmul: tile does not fit shared memory");
+  static const bool force_rowcopy = [] { const char* v = std::getenv("B200_TC_ROWCOPY"); return v && v[0] == '1'; }();
+  const int tr = 16 * p.R;
+  p.w_rowcopy = (force_rowcopy || (tr < TC_M ? TC_M % tr : tr % TC_M)) ? 1 : 0;
+  TcMaps maps;
+  std::memset(&maps, 0, sizeof(maps));
+  {  // activation tiles: 64 elements along K x NT tokens, written in the 128-byte-swizzle layout; tokens beyond T read as zero
+    const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+    const cuuint64_t gstr[1] = {(cuuint64_t)p.K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)NT};
+    encode_map(&maps.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.x16, gdim, gstr, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (!p.w_rowcopy) {
+    // packed units: (32-bit words of a stage row, rows of an image tile, slabs, image tiles); box = one unit x 128 rows
+    for (int s = 0; s < p.nseg; ++s) {
+      const GemvSeg& sg = p.seg[s];
+      const cuuint32_t ub = (cuuint32_t)gemv_unit_bytes(sg.type);
+      const cuuint32_t box[4] = {ub / 4, (cuuint32_t)std::min(tr, TC_M), 1, (cuuint32_t)std::max(1, TC_M / tr)};
+      for (int last = 0; last < 2; ++last) {
+        if (!last && p.nslab == 1) continue;
+        const cuuint64_t rs = (cuuint64_t)(last ? sg.RS_last : sg.RS);
+        const cuuint64_t gdim[4] = {rs / 4, (cuuint64_t)tr, (cuuint64_t)(last ? 1 : p.nslab - 1), (cuuint64_t)sg.tiles};
+        const cuuint64_t gstr[3] = {rs, (cuuint64_t)(last ? sg.stage_bytes_last : sg.stage_bytes), (cuuint64_t)sg.tile_bytes};
+        const uint8_t* base = sg.img + (last ? (size_t)(p.nslab - 1) * sg.stage_bytes : 0);
+        encode_map(&maps.w[s][last], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, base, gdim, gstr, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+      }
+    }
+  }
   dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT, p.ksplit);
-  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT), st>>>(p, tm);
+  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT, p.a_stages, p.b_stages, p.w_stages, p.w_stage_bytes), st>>>(p, maps);
   CK(cudaGetLastError());
 }
 

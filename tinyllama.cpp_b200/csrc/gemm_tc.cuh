@@ -4,17 +4,22 @@
 // (model.cpp:2141-2249). "Swap-AB": the weight rows are the M side of the MMA (128 per CTA tile),
 // the tokens the N side (16..256 per tile).
 //
-// A CTA (544 threads) owns one tile of 128 rows x NT tokens and walks K in steps of 64 elements.
-// Three roles meet only on mbarriers; there is no block-wide barrier inside the K loop:
-//   * sixteen warps dequantise: a thread owns (row, 16-element quarter of the step), fetches its
-//     packed bytes one 256-element block ahead, straight from the stage images, converts them to
-//     fp16 and stores them into one of four weight stages (128 rows x 128 bytes) in the K-major
+// A CTA (608 threads) owns one tile of 128 rows x NT tokens and walks K in steps of 64 elements.
+// Five roles meet only on mbarriers; there is no block-wide barrier inside the K loop:
+//   * a weight-producer warp brings the packed units of the tile's 128 rows, one 256-element block
+//     per tensor copy (cp.async.bulk.tensor.4d over the stage images), into a ring of 1-4 stages;
+//   * sixteen warps dequantise: a thread owns (row, 16-element quarter of the step), copies its
+//     share of a landed block from the ring into registers (which frees the stage), converts it to
+//     fp16 and stores it into one of 4 or 8 weight stages (128 rows x 128 bytes) in the K-major
 //     128-byte-swizzle layout the MMA unit reads from shared memory;
-//   * one lane of the control warp moves the matching slices of the fp16 activations with TMA
-//     (cp.async.bulk.tensor.2d, same swizzle, tokens beyond T read as zero) into four activation
-//     stages, three steps ahead, and issues four tcgen05.mma (M=128, N=NT, K=16, kind::f16) per
-//     step that accumulate into a 128-lane x NT-column fp32 tile in tensor memory; tcgen05.commit
-//     tells the dequantising warps when a stage may be overwritten;
+//   * one lane of an activation-producer warp moves the matching slices of the fp16 activations
+//     with TMA (cp.async.bulk.tensor.2d, same swizzle, tokens beyond T read as zero) into 2-4
+//     activation stages as soon as the MMAs that read a stage have completed;
+//   * one lane of the MMA warp issues four tcgen05.mma (M=128, N=NT, K=16, kind::f16) per step that
+//     accumulate into a 128-lane x NT-column fp32 tile in tensor memory, and does nothing else:
+//     a single thread's dependent instruction stream is slow (measured: with the activation loads,
+//     stage arithmetic and descriptor construction in this thread it needed 1 100 cycles per step and
+//     everyone else waited for it); tcgen05.commit tells the other roles when a stage may be reused;
 //   * after the last step the sixteen warps read their TMEM lanes back (tcgen05.ld 32x32b:
 //     thread = weight row, registers = tokens) and run the same epilogues as the matvec kernel
 //     (store, residual add, RoPE scatter, SwiGLU).
@@ -33,7 +38,7 @@ namespace b200 {
 constexpr int TC_M = 128;        // weight rows per CTA tile (the MMA's M)
 constexpr int TC_KC = 64;        // elements along K per shared-memory stage: one 128-byte swizzled row of fp16
 constexpr int TC_WORKERS = 512;   // sixteen dequantising warps: thread = (weight row, 16-element quarter of the 64-element step)
-constexpr int TC_THREADS = TC_WORKERS + 32;  // + one control warp
+constexpr int TC_THREADS = TC_WORKERS + 96;  // + the MMA warp, the weight-producer warp and the activation-producer warp
 constexpr int TC_MAX_N = 256;     // tokens per CTA tile
 
 struct TcParams {
@@ -55,6 +60,10 @@ struct TcParams {
   const int* positions;           // [T]
   int head_dim, max_pos;
   int ntiles_m;                   // 128-row tiles over all segments
+  int a_stages;                   // weight-tile stages: 4 or 8
+  int b_stages;                   // activation stages (2 to 4)
+  int w_stages, w_stage_bytes;    // packed-weight ring: stages of 128 rows x unit bytes
+  int w_rowcopy;                  // 1: the producer copies row by row (geometries a tensor map cannot describe)
   int ksplit, kblocks;            // split-K: CTA z takes 256-element blocks [z*kblocks, (z+1)*kblocks) and stores to y + z*T*y_stride (EPI_STORE only)
   int* error_flag;
 };
@@ -115,23 +124,12 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 // 16-byte chunk c (0..7) of row r in a swizzled tile
 __device__ __forceinline__ uint32_t tc_swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
-// Address of unit (image row, block) inside a segment's stage images, and of the row's Q6_K scale
-// array (see GemvGeom): the batched kernel reads the same images the matvec kernel streams.
+// Where a thread finds one unit (image row, block) in the packed-weight ring, and the block's
+// Q6_K scale: the batched kernel reads the same stage images the matvec kernel streams (GemvGeom).
 struct TcUnit {
   const uint8_t* unit;
   const uint8_t* d;  // Q6_K: this block's fp16 d
 };
-__device__ __forceinline__ TcUnit tc_locate(const TcParams& p, const GemvSeg& sg, int irow, int blk) {
-  const int tr = 16 * p.R;
-  const int tile = irow / tr, rr = irow - tile * tr;
-  const int slab = blk / p.S, bb = blk - slab * p.S;
-  const bool last = slab == p.nslab - 1;
-  const uint8_t* rowp = sg.img + (size_t)tile * sg.tile_bytes + (size_t)slab * sg.stage_bytes + (size_t)rr * (last ? sg.RS_last : sg.RS);
-  TcUnit u;
-  u.unit = rowp + (size_t)bb * gemv_unit_bytes(sg.type);
-  u.d = rowp + (last ? sg.d_off_last : sg.d_off) + 2 * bb;
-  return u;
-}
 
 // The packed bytes of one 256-element block that one thread needs for the block's four K steps,
 // fetched one block ahead of their use so that the loads overlap the previous block's work. A
@@ -145,21 +143,21 @@ struct TcRaw {
 
 __device__ __forceinline__ void tc_fetch(int type, const TcUnit& u, int half, int sub, TcRaw& t) {
   if (type == T_Q4_K) {
-    t.r[0] = __ldg(reinterpret_cast<const uint4*>(u.unit));
+    t.r[0] = *reinterpret_cast<const uint4*>(u.unit);
 #pragma unroll
-    for (int kc = 0; kc < 4; ++kc) t.r[1 + kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc + 16 * sub));
+    for (int kc = 0; kc < 4; ++kc) t.r[1 + kc] = *reinterpret_cast<const uint4*>(u.unit + 16 + 32 * kc + 16 * sub);
   } else if (type == T_Q6_K) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      t.r[hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half + 16 * sub));
-      t.r[2 + hh] = __ldg(reinterpret_cast<const uint4*>(u.unit + 128 + 32 * hh + 16 * sub));
+      t.r[hh] = *reinterpret_cast<const uint4*>(u.unit + 64 * hh + 32 * half + 16 * sub);
+      t.r[2 + hh] = *reinterpret_cast<const uint4*>(u.unit + 128 + 32 * hh + 16 * sub);
     }
-    t.r[4] = __ldg(reinterpret_cast<const uint4*>(u.unit + 192));
-    t.r[5].x = __ldg(reinterpret_cast<const uint16_t*>(u.d));
+    t.r[4] = *reinterpret_cast<const uint4*>(u.unit + 192);
+    t.r[5].x = *reinterpret_cast<const uint16_t*>(u.d);
   } else {
 #pragma unroll
-    for (int kc = 0; kc < 4; ++kc) t.r[kc] = __ldg(reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half) + 16 * sub));
-    t.r[4] = __ldg(reinterpret_cast<const uint4*>(u.unit + 256));
+    for (int kc = 0; kc < 4; ++kc) t.r[kc] = *reinterpret_cast<const uint4*>(u.unit + 32 * (2 * kc + half) + 16 * sub);
+    t.r[4] = *reinterpret_cast<const uint4*>(u.unit + 256);
   }
 }
 
@@ -235,14 +233,26 @@ __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, i
   w[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
 }
 
-constexpr int TC_B_STAGES = 4;  // activation tiles in flight (TMA)
-constexpr int TC_A_STAGES = 4;  // weight-tile stages: one per K step of a 256-element block
+constexpr int TC_B_STAGES = 4;  // at most: activation tiles in flight (TMA)
+constexpr int TC_A_STAGES = 8;  // at most: weight-tile stages (four per 256-element block; one or two blocks deep)
+constexpr int TC_W_STAGES = 4;  // at most: packed-weight stages in flight (TMA)
+constexpr int TC_D_BYTES = 2 * TC_M * 32;  // Q6_K block scales of a tile's rows for the current and the next slab
+
+// Tensor maps of one launch: the fp16 activations and, per segment, the packed units of its stage
+// images seen as a 4-D array (bytes of a stage row / rows of an image tile / slabs / image tiles) -
+// one map for the full slabs and one for the last slab of every tile, whose rows are shorter.
+struct alignas(64) TcMaps {
+  CUtensorMap act;
+  CUtensorMap w[3][2];
+};
 
 struct TcShared {
   unsigned long long a_full[TC_A_STAGES];  // all dequantising warps have stored their part of the weight tile
   unsigned long long b_full[TC_B_STAGES];  // the activation tile has landed (TMA transaction bytes)
   unsigned long long mma_done[TC_A_STAGES];  // the MMAs that read weight stage i (and its activation stage) have completed
   unsigned long long done_bar;             // all MMAs of the tile have completed
+  unsigned long long w_full[TC_W_STAGES];  // the packed units of a block (and, at a slab start, the Q6_K scales) have landed
+  unsigned long long w_empty[TC_W_STAGES]; // all dequantising warps have copied their part of the stage into registers
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -262,20 +272,33 @@ __device__ __forceinline__ void tc_tma_load_2d(void* dst, const void* tmap, int 
                : "memory");
 }
 
-// grid = (128-row tiles over all segments, token tiles of NT, K splits); 544 threads: warps 0-15
-// dequantise the weight tile (thread = row x 16-element quarter), warp 16 moves the activation tiles
-// with TMA and issues the MMAs. No block-wide barrier inside the K loop: the roles meet on mbarriers.
-// dynamic shared memory (1024-byte aligned): 4 weight stages of 16 KB + 4 activation stages of NT x 128 bytes
-__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT) { return 1024 + TC_A_STAGES * (size_t)TC_M * 128 + TC_B_STAGES * (size_t)NT * 128; }
+// grid = (128-row tiles over all segments, token tiles of NT, K splits); 608 threads: warps 0-15
+// dequantise the weight tile (thread = row x 16-element quarter), warp 16 issues the MMAs, warp 17
+// moves the packed weights, warp 18 the activation tiles. Dynamic shared memory (1024-byte aligned):
+// 4 or 8 weight stages of 16 KB, 2-4 activation stages of NT x 128 bytes, the packed-weight ring,
+// the Q6_K scale buffers.
+__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT, int a_stages, int b_stages, int w_stages, int w_stage_bytes) {
+  return 1024 + a_stages * (size_t)TC_M * 128 + b_stages * (size_t)NT * 128 + (size_t)w_stages * w_stage_bytes + TC_D_BYTES;
+}
+constexpr int TC_SMEM_MAX = 226 * 1024;  // dynamic part; the barriers live in static shared memory
 
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap tmap) {
+// 4-D tiled TMA load of the packed units of 128 rows of one block (no swizzle: rows land back to back)
+__device__ __forceinline__ void tc_tma_load_4d(void* dst, const void* tmap, int c0, int c1, int c2, int c3, void* bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p, const __grid_constant__ TcMaps maps) {
   extern __shared__ uint8_t tc_smem_raw[];
   __shared__ TcShared sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* const Abase = smem;                                 // [4][128 rows][128 B]
-  uint8_t* const Bbase = smem + TC_A_STAGES * TC_M * 128;      // [4][NT rows][128 B]
+  uint8_t* const Bbase = smem + p.a_stages * TC_M * 128;      // [b_stages][NT rows][128 B]
   const uint32_t b_stage_bytes = (uint32_t)p.NT * 128;
+  uint8_t* const Wbase = Bbase + (size_t)p.b_stages * b_stage_bytes;       // [w_stages][128 rows][unit bytes]
+  uint8_t* const Dbase = Wbase + (size_t)p.w_stages * p.w_stage_bytes;     // [2][128 rows][32 B]
   // ---- which rows, which tokens, which part of K ----
   int seg = 0, mt = blockIdx.x;
   while (seg + 1 < p.nseg && mt >= (p.seg[seg].rows + TC_M - 1) / TC_M) { mt -= (p.seg[seg].rows + TC_M - 1) / TC_M; ++seg; }
@@ -287,6 +310,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
   if (tid == 0) {
     for (int i = 0; i < TC_A_STAGES; ++i) { mbar_init(&sh.a_full[i], TC_WORKERS / 32); mbar_init(&sh.mma_done[i], 1); }
     for (int i = 0; i < TC_B_STAGES; ++i) mbar_init(&sh.b_full[i], 1);
+    for (int i = 0; i < TC_W_STAGES; ++i) { mbar_init(&sh.w_full[i], 1); mbar_init(&sh.w_empty[i], TC_WORKERS / 32); }
     mbar_init(&sh.done_bar, 1);
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -298,57 +322,114 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
   const uint32_t tmem_d = sh.tmem_base;
 
   if (warp == TC_WORKERS / 32) {
-    // ---- control warp: one lane moves activation tiles and issues the MMAs ----
+    // ---- MMA warp: one lane waits for a weight stage and an activation stage and issues the step's
+    //      four MMAs. Its instruction stream is the kernel's critical path (one thread, every
+    //      instruction waits for the one before), so it is kept to the bare minimum: running stage
+    //      counters instead of divisions, descriptors advanced by constants, loads left to others ----
     if (lane == 0) {
       const uint32_t idesc = tc_idesc(p.NT);
-      auto load_b = [&](int s) {  // activation tile of step s into stage s % 4
-        void* bar = &sh.b_full[s % TC_B_STAGES];
-        mbar_expect_tx(bar, b_stage_bytes);
-        tc_tma_load_2d(Bbase + (size_t)(s % TC_B_STAGES) * b_stage_bytes, &tmap, (4 * blk0 + s) * TC_KC, t0, bar);
-      };
-      for (int s = 0; s < nsteps && s < TC_B_STAGES - 1; ++s) load_b(s);
-      for (int s = 0; s < nsteps; ++s) {
-        // stage (s + 3) % 4 was read by the MMAs of step s - 1: refill it three steps ahead once they are done
-        if (s + TC_B_STAGES - 1 < nsteps) {
-          if (s >= 1) tc_wait(p, &sh, &sh.mma_done[(s - 1) % TC_A_STAGES], (uint32_t)(((s - 1) / TC_A_STAGES) & 1));
-          load_b(s + TC_B_STAGES - 1);
-        }
-        tc_wait(p, &sh, &sh.a_full[s % TC_A_STAGES], (uint32_t)((s / TC_A_STAGES) & 1));
-        tc_wait(p, &sh, &sh.b_full[s % TC_B_STAGES], (uint32_t)((s / TC_B_STAGES) & 1));
+      const int nb = p.b_stages, na = p.a_stages;
+      const uint64_t adesc0 = tc_smem_desc(smem_u32(Abase)), bdesc0 = tc_smem_desc(smem_u32(Bbase));
+      const uint64_t a_step = (uint64_t)((TC_M * 128) >> 4), b_step = (uint64_t)(b_stage_bytes >> 4);
+      int sa = 0, sb = 0;
+      uint32_t pa = 0, pb = 0;
+      uint64_t adesc = adesc0, bdesc = bdesc0;
+      bool ok = !*(volatile int*)&sh.abort_flag;
+#pragma unroll 1
+      for (int s = 0; s < nsteps && ok; ++s) {
+        ok = mbar_wait(&sh.a_full[sa], pa) && mbar_wait(&sh.b_full[sb], pb);
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t a0 = smem_u32(Abase + (size_t)(s % TC_A_STAGES) * TC_M * 128);
-        const uint32_t b0 = smem_u32(Bbase + (size_t)(s % TC_B_STAGES) * b_stage_bytes);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          tc_mma_f16(tmem_d, tc_smem_desc(a0 + 32 * k4), tc_smem_desc(b0 + 32 * k4), idesc, (s | k4) ? 1u : 0u);
-        tc_commit(&sh.mma_done[s % TC_A_STAGES]);
-        if (s == nsteps - 1) tc_commit(&sh.done_bar);
+        for (int k4 = 0; k4 < 4; ++k4) tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (s | k4) ? 1u : 0u);  // 16 elements along K = 32 bytes = 2 descriptor units
+        tc_commit(&sh.mma_done[sa]);
+        adesc += a_step; bdesc += b_step;
+        if (++sa == na) { sa = 0; pa ^= 1u; adesc = adesc0; }
+        if (++sb == nb) { sb = 0; pb ^= 1u; bdesc = bdesc0; }
+      }
+      if (!ok) tc_fail(p, &sh);
+      tc_commit(&sh.done_bar);
+    }
+    __syncwarp();
+  } else if (warp == TC_WORKERS / 32 + 2) {
+    // ---- activation producer: tile of step s into stage s % nb as soon as the MMAs of step s - nb have read it ----
+    if (lane == 0) {
+      const int nb = p.b_stages, na = p.a_stages;
+#pragma unroll 1
+      for (int s = 0; s < nsteps; ++s) {
+        if (s >= nb) tc_wait(p, &sh, &sh.mma_done[(s - nb) % na], (uint32_t)(((s - nb) / na) & 1));
+        void* bar = &sh.b_full[s % nb];
+        mbar_expect_tx(bar, b_stage_bytes);
+        tc_tma_load_2d(Bbase + (size_t)(s % nb) * b_stage_bytes, &maps.act, (4 * blk0 + s) * TC_KC, t0, bar);
+      }
+    }
+    __syncwarp();
+  } else if (warp == TC_WORKERS / 32 + 1) {
+    // ---- weight producer: one tensor copy per 256-element block brings the packed units of the
+    //      tile's 128 rows into the ring (rows beyond the images read as zero); at the start of a
+    //      slab the lanes also copy the rows' Q6_K block scales ----
+    const int ub = gemv_unit_bytes(sg.type), tr = 16 * p.R, nw = p.w_stages;
+    const bool q6 = sg.type == T_Q6_K;
+#pragma unroll 1
+    for (int blk = 0; blk < nblocks; ++blk) {
+      const int gb = blk0 + blk, slab = gb / p.S, bb = gb - slab * p.S;
+      const bool last = slab == p.nslab - 1;
+      const int stage = blk % nw;
+      void* bar = &sh.w_full[stage];
+      if (blk >= nw && lane == 0) tc_wait(p, &sh, &sh.w_empty[stage], (uint32_t)((blk / nw - 1) & 1));
+      __syncwarp();
+      const bool with_d = q6 && (bb == 0 || blk == 0);
+      const uint32_t dbytes = (uint32_t)((2 * (last ? p.S_last : p.S) + 15) / 16 * 16);
+      if (lane == 0) {
+        mbar_expect_tx(bar, (uint32_t)(TC_M * ub) + (with_d ? TC_M * dbytes : 0u));
+        if (!p.w_rowcopy)
+          tc_tma_load_4d(Wbase + (size_t)stage * p.w_stage_bytes, &maps.w[seg][last ? 1 : 0], bb * ub / 4, row0 % tr, last ? 0 : slab, row0 / tr, bar);
+      }
+      if (with_d || p.w_rowcopy) {
+        for (int r = lane; r < TC_M; r += 32) {
+          const int irow = min(row0 + r, sg.rows - 1);  // rows past the segment repeat the last one; their results are dropped
+          const int tile = irow / tr, rr = irow - tile * tr;
+          const uint8_t* rowp = sg.img + (size_t)tile * sg.tile_bytes + (size_t)slab * sg.stage_bytes + (size_t)rr * (last ? sg.RS_last : sg.RS);
+          if (p.w_rowcopy) bulk_g2s(Wbase + (size_t)stage * p.w_stage_bytes + (size_t)r * ub, rowp + (size_t)bb * ub, (uint32_t)ub, bar);
+          if (with_d) bulk_g2s(Dbase + (size_t)(slab & 1) * (TC_M * 32) + (size_t)r * 32, rowp + (last ? sg.d_off_last : sg.d_off), dbytes, bar);
+        }
       }
     }
     __syncwarp();
   } else {
     // ---- dequantising warps: thread = (weight row, 16-element quarter of the step) ----
     const int my_row = tid & (TC_M - 1), my_half = (tid >> 8) & 1, my_sub = (tid >> 7) & 1;
-    const int irow = min(row0 + my_row, sg.rows - 1);  // rows past the segment repeat the last one; their results are dropped
-    TcRaw cur, nxt;
-    tc_fetch(sg.type, tc_locate(p, sg, irow, blk0), my_half, my_sub, cur);
+    const int ub = gemv_unit_bytes(sg.type), nw = p.w_stages;
+    TcRaw cur;
 #pragma unroll 1
     for (int blk = 0; blk < nblocks; ++blk) {
-      if (blk + 1 < nblocks) tc_fetch(sg.type, tc_locate(p, sg, irow, blk0 + blk + 1), my_half, my_sub, nxt);  // lands while this block is worked on
+      {
+        const int gb = blk0 + blk, slab = gb / p.S, bb = gb - slab * p.S;
+        const int stage = blk % nw;
+        tc_wait(p, &sh, &sh.w_full[stage], (uint32_t)((blk / nw) & 1));
+        TcUnit u;
+        u.unit = Wbase + (size_t)stage * p.w_stage_bytes + (size_t)my_row * ub;
+        u.d = Dbase + (size_t)(slab & 1) * (TC_M * 32) + (size_t)my_row * 32 + 2 * bb;
+        tc_fetch(sg.type, u, my_half, my_sub, cur);  // the thread's share of the block, into registers
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.w_empty[stage]);  // the stage may be refilled
+      }
+#pragma unroll
+      const int adepth = p.a_stages >> 2;            // blocks the weight-tile ring holds
+      const int abase = (blk % adepth) * 4, alap = blk / adepth;
 #pragma unroll
       for (int kc = 0; kc < 4; ++kc) {
-        uint8_t* A = Abase + (size_t)kc * TC_M * 128;  // stage = step % 4 = kc
+        uint8_t* A = Abase + (size_t)(abase + kc) * TC_M * 128;  // stage = step % a_stages
         uint4 w[2];
         tc_dequant16(sg.type, cur, kc, my_half, my_sub, w);
-        // the MMAs that read this stage four steps ago must be done before it is overwritten
-        if (blk >= 1) tc_wait(p, &sh, &sh.mma_done[kc], (uint32_t)((blk - 1) & 1));
+        // the MMAs that read this stage a ring lap ago must be done before it is overwritten
+        if (alap >= 1) tc_wait(p, &sh, &sh.mma_done[abase + kc], (uint32_t)((alap - 1) & 1));
 #pragma unroll
         for (int c = 0; c < 2; ++c) *reinterpret_cast<uint4*>(A + tc_swz(my_row, my_half * 4 + my_sub * 2 + c)) = w[c];
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core's reads
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.a_full[kc]);  // one arrival per warp: 512 arrivals on one barrier word would serialise
+        if (lane == 0) mbar_arrive(&sh.a_full[abase + kc]);  // one arrival per warp: 512 arrivals on one barrier word would serialise
       }
-      cur = nxt;
     }
   }
   // ---- epilogue: warp w reads TMEM lanes 32*(w & 3) .. +31 (= weight rows), the four warp groups split the tokens ----
