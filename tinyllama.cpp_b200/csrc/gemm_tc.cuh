@@ -169,6 +169,14 @@ __device__ __forceinline__ float byte_to_float(uint32_t v, int k, float bias) {
   return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 | k)) - bias;
 }
 
+// Byte k of `v` (its top two bits clear, bit 7 pre-set by the caller: v = q | 0x80 per byte) as the
+// float 1 + q / 128: the byte lands in mantissa bits 16..22 under the exponent of 1.0 (its bit 7 is
+// the exponent's lowest bit). One PRMT, and the affine map back to q folds into the FMA that applies
+// the scale: scale * (q - off) = (128 scale) * X - (128 + off) * scale, X = 1 + q/128.
+__device__ __forceinline__ float byte_to_unit_float(uint32_t v, int k) {
+  return __uint_as_float(__byte_perm(v, 0x3F000000u, 0x7044 | (k << 8)));
+}
+
 // Dequantises the thread's 16 elements of step kc (elements [64*kc + 32*half + 16*sub, +16) of the
 // block held in `t`) to fp16: two 16-byte chunks w[0..1] (eight halves each). kc is a compile-time
 // constant at every call site (the K steps of a block are unrolled). Each weight is computed in
@@ -196,12 +204,15 @@ __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, i
       mn = (q(sb + 4) >> 4) | ((q(sb) >> 6) << 4);
     }
     const float d1 = dm.x * (float)sc, m1 = dm.y * (float)mn;
+    // d1 * q - m1 = D * X - (D + m1), D = 128 d1 (exact), X = 1 + q/128: the constant's rounding is 2^-24 of
+    // 128 d1, far below the fp16 rounding of the result
+    const float D = 128.0f * d1, C = -(D + m1);
     const int shift = half ? 4 : 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // word i: its bytes 4i .. 4i+3 -> elements 4i .. 4i+3
-      const uint32_t word = (u4_word(t.r[1 + kc], i) >> shift) & 0x0F0F0F0Fu;
+      const uint32_t word = ((u4_word(t.r[1 + kc], i) >> shift) & 0x0F0F0F0Fu) | 0x80808080u;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) v[4 * i + k] = fmaf(d1, byte_to_float(word, k, 8388608.0f), -m1);
+      for (int k = 0; k < 4; ++k) v[4 * i + k] = fmaf(D, byte_to_unit_float(word, k), C);
     }
   } else if (type == T_Q6_K) {
     const int hh = kc >> 1, j = 2 * (kc & 1) + half;  // 128-element half, which of q1..q4
@@ -209,14 +220,15 @@ __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, i
     // sub-block scale 8hh + 2j + sub (signed byte)
     const uint32_t sw = u4_word(t.r[4], 2 * hh + (j >> 1));
     const float sc = d * (float)(int)(int8_t)((sw >> (16 * (j & 1) + 8 * sub)) & 0xFF);
+    const float S = 128.0f * sc, C = -160.0f * sc;  // sc * (q - 32) = S * X - (128 + 32) sc, X = 1 + q/128 (both products exact scalings of sc)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t lword = u4_word(t.r[hh], i), hword = u4_word(t.r[2 + hh], i);
       const uint32_t nib = ((j >> 1) ? (lword >> 4) : lword) & 0x0F0F0F0Fu;
       const uint32_t top = (j == 0 ? (hword << 4) : j == 1 ? (hword << 2) : j == 2 ? hword : (hword >> 2)) & 0x30303030u;
-      const uint32_t six = nib | top;
+      const uint32_t six = nib | top | 0x80808080u;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) v[4 * i + k] = sc * byte_to_float(six, k, 8388640.0f);  // removes the format's offset of 32 as well
+      for (int k = 0; k < 4; ++k) v[4 * i + k] = fmaf(S, byte_to_unit_float(six, k), C);  // sc * (q - 32)
     }
   } else {  // Q8_0 unit: 8 x 32 quants, then 8 fp16 d
     const int b32 = 2 * kc + half;
