@@ -29,6 +29,8 @@ WORKLOADS = {
     "c2-tinyllama-q4km-bs1": ("tinyllama-1.1b", 1, 1, 512, "i8"),
     "c3-llama2-7b-q4km-bs1": ("llama2-7b", 1, 1, 1024, "i8"),
     "c3-llama2-7b-q4km-bs16": ("llama2-7b", 1, 16, 1024, "i8"),
+    # ragged contexts: prompt lengths uniform in [256, 4096] from PCG64(99)
+    "c4-llama3-8b-q6k-bs64": ("llama3-8b", 2, 64, (256, 4096), "i8"),
     "tiny": ("tiny", 1, 1, 16, "i8"),
 }
 DEFAULT_WORKLOAD = "c3-llama2-7b-q4km-bs1"
@@ -87,8 +89,17 @@ def model_path(pkg, shape, scheme):
     return path
 
 
+def prompt_lengths(batch, prompt_len):
+    """One length per sequence: a fixed length, or (lo, hi) = ragged lengths uniform in [lo, hi] from PCG64(99)."""
+    if isinstance(prompt_len, tuple):
+        lo, hi = prompt_len
+        return [int(v) for v in np.random.Generator(np.random.PCG64(99)).integers(lo, hi + 1, batch)]
+    return [int(prompt_len)] * batch
+
+
 def prompts(batch, n, vocab):
-    return [np.random.Generator(np.random.PCG64(4321 + s)).integers(0, vocab, n).astype(np.int32) for s in range(batch)]
+    lens = prompt_lengths(batch, n)
+    return [np.random.Generator(np.random.PCG64(4321 + s)).integers(0, vocab, lens[s]).astype(np.int32) for s in range(batch)]
 
 
 def dist_env():
@@ -170,7 +181,7 @@ def main():
         dist.broadcast(idt, src=0)
         nccl_id = bytes(idt.cpu().tolist())
     eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if kv == "i8" else pkg.KV_F32, max_seqs=batch,
-                               max_ctx=prompt_len + args.steps + warmup + 80, act_planes=args.planes, device=local_rank,
+                               max_ctx=max(prompt_lengths(batch, prompt_len)) + args.steps + warmup + 80, act_planes=args.planes, device=local_rank,
                                tp_rank=rank, tp_size=world, nccl_id=nccl_id)
     t_load = time.perf_counter() - t_load
     vocab = eng.vocab
@@ -180,17 +191,21 @@ def main():
     for s in range(batch):
         first.append(int(eng.prefill(pr[s], slot=s).argmax()))
     t_prefill = time.perf_counter() - t_prefill
-    pos = prompt_len
+    lens = prompt_lengths(batch, prompt_len)
+    pos = 0  # steps decoded so far; sequence s is at position lens[s] + pos
+
+    def at(p):
+        return [n + p for n in lens]
 
     # ---- warm-up, then the timed device-resident loop ----
-    out, _ = eng.generate_greedy(first, [pos] * batch, warmup)
+    out, _ = eng.generate_greedy(first, at(pos), warmup)
     pos += warmup
     nxt = out[-1].copy()
     if dist:
         dist.barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    out, ms = eng.generate_greedy(nxt, [pos] * batch, args.steps)
+    out, ms = eng.generate_greedy(nxt, at(pos), args.steps)
     clocks = sampler.finish()
     pos += args.steps
     if dist:
@@ -204,11 +219,11 @@ def main():
     # ---- end to end through the C ABI with host buffers: token ids in, logits out, host argmax ----
     e2e_steps = min(args.steps, 64)
     toks = out[-1].copy()
-    eng.decode(toks, [pos] * batch)  # graph already warm; one untimed call
+    eng.decode(toks, at(pos))  # graph already warm; one untimed call
     pos += 1
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        logits, _ = eng.decode(toks, [pos + i] * batch, want_logits=True, want_argmax=False)
+        logits, _ = eng.decode(toks, at(pos + i), want_logits=True, want_argmax=False)
         toks = logits.argmax(axis=1).astype(np.int32)
     e2e_dt = time.perf_counter() - t0
     e2e_tps = batch * e2e_steps / e2e_dt
@@ -236,9 +251,9 @@ def main():
         tot = sum(ncu_mb[k] * 1e6 * kinds[k][1] for k in ncu_mb) + ratio * kern["lm_head"]["bytes"]
         traffic = int(tot / gemv_launches)
     achieved = ksum_b / ksum_t / 1e3  # GB/s
-    ctx_mid = prompt_len + warmup + args.steps / 2.0
+    ctx_sum_mid = sum(lens) + batch * (warmup + args.steps / 2.0)  # context positions read per step, over all sequences, mid-run
     # per-rank shares add up to the whole model over the ranks (norm vectors are replicated: negligible)
-    step_bytes = world * (st["weight_bytes"] + batch * ctx_mid * st["kv_bytes_per_position"]) + batch * 4 * eng.hidden
+    step_bytes = world * (st["weight_bytes"] + ctx_sum_mid * st["kv_bytes_per_position"]) + batch * 4 * eng.hidden
     step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9 / world  # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "traffic": traffic, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
@@ -250,8 +265,8 @@ def main():
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": f"i{8 * args.planes} activations x packed int weights, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len, "kv_cache": kv,
-                       "context_during_timing": [prompt_len + warmup, prompt_len + warmup + args.steps],
+            "config": {"workload": args.workload, "batch": batch, "prompt_len": list(prompt_len) if isinstance(prompt_len, tuple) else prompt_len,
+                       "kv_cache": kv, "context_during_timing": [min(lens) + warmup, max(lens) + warmup + args.steps],
                        "parallelism": "single GPU" if world == 1 else f"tp{world} (column-split QKV/gate/up/head, row-split O/down, " +
                                       ("one-shot all-reduce over peer memory inside the matvec kernels" if st["launches_per_step"] == 3 + 5 * L
                                        else "NCCL all-reduce") + ", NCCL all-gather of logits)",

@@ -295,6 +295,38 @@ def test_batch16_decode_takes_tensor_core_path(pkg, tiny_models, scheme, kv):
     eng.close()
 
 
+@pytest.mark.parametrize("kv", ["f32", "i8"])
+def test_batch_decode_grouped_query_attention_long_contexts(pkg, tiny_models, kv):
+    """Batched decode of a grouped-query model (2 query heads per KV head) with ragged contexts of up to two
+    64-key tiles: the tensor-core attention that serves a whole group per CTA, all four key quarters and the
+    merge of their partial softmaxes. Logits against the oracle: 2e-2 absolute (FP32 cache); with the INT8
+    cache the prompt's K/V rows come from fp16 matmuls and may round to a neighbouring int8 step, so the
+    bound is relative to the largest logit as in the prompt tests."""
+    B = 16
+    kvd = pkg.KV_I8 if kv == "i8" else pkg.KV_F32
+    eng = pkg.Engine.from_gguf(tiny_models[1], max_seqs=B, kv_dtype=kvd)
+    orc = ol.OracleModel.from_gguf(tiny_models[1], max_seqs=B, kv_int8=(kv == "i8"))
+    rng = np.random.default_rng(23)
+    lens = [int(n) for n in rng.integers(1, 118, B)]
+    lens[0], lens[1], lens[2] = 63, 64, 117
+    for s in range(B):
+        ids = rng.integers(0, 512, lens[s])
+        eng.prefill(ids, slot=s)
+        orc.prefill(ids, seq=s)
+    toks = [int(t) for t in rng.integers(0, 512, B)]
+    pos = list(lens)
+    for step in range(3):
+        logits, amax = eng.decode(toks, pos)
+        nxt = []
+        for b in range(B):
+            ref = orc.decode(toks[b], pos[b], seq=b)
+            tol = 2e-2 if kv == "f32" else max(2e-2, 1.5e-2 * float(np.abs(ref).max()))
+            assert np.abs(logits[b] - ref).max() <= tol, (b, pos[b])
+            nxt.append(int(ref.argmax()))
+        toks, pos = nxt, [p + 1 for p in pos]
+    eng.close()
+
+
 def test_forward_from_hidden_state(pkg, tiny_models):
     """b200_forward mirrors TinyLlamaModel::forward: hidden vector in, logits out, input updated in place."""
     eng = pkg.Engine.from_gguf(tiny_models[1])

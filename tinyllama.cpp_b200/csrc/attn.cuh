@@ -346,11 +346,13 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
 }
 
 // Prompt ingestion: appends the K and V rows of n tokens to the cache before their attention runs
-// (same arithmetic as the append inside attn_item). grid = (tokens, kv heads, 2: K | V), one warp each.
-__global__ void kv_append_kernel(const float* __restrict__ kv_new, int kvn_stride, const int* __restrict__ positions,
-                                 const int* __restrict__ slots, int nkv, int hd, int max_ctx, int kv_i8, void* k_cache, void* v_cache,
-                                 float* k_scale, float* v_scale) {
-  const int t = blockIdx.x, kvh = blockIdx.y, which = blockIdx.z, lane = threadIdx.x;
+// (same arithmetic as the append inside attn_item). grid = (tokens, ceil(kv heads / 4), 2: K | V), 128 threads: one warp per row.
+constexpr int KVA_WARPS = 4;
+__global__ void __launch_bounds__(32 * KVA_WARPS) kv_append_kernel(const float* __restrict__ kv_new, int kvn_stride, const int* __restrict__ positions,
+                                                                   const int* __restrict__ slots, int nkv, int hd, int max_ctx, int kv_i8, void* k_cache,
+                                                                   void* v_cache, float* k_scale, float* v_scale) {
+  const int t = blockIdx.x, kvh = blockIdx.y * KVA_WARPS + (threadIdx.x >> 5), which = blockIdx.z, lane = threadIdx.x & 31;
+  if (kvh >= nkv) return;
   const float* src = kv_new + (size_t)t * kvn_stride + (which ? nkv * hd : 0) + kvh * hd;
   const size_t crow = ((size_t)slots[t] * nkv + kvh) * max_ctx + positions[t];
   void* cache = which ? v_cache : k_cache;

@@ -280,4 +280,219 @@ __global__ void __launch_bounds__(PFA_THREADS, 2) attn_prefill_kernel(const Pref
   }
 }
 
+// Batched decode attention for grouped-query models: one CTA per (sequence, KV head) serves all
+// G = n_heads / n_kv_heads query heads of the group (G <= 8), so every K/V row of the sequence is
+// read once per step instead of once per query head. Same tiles and conversions as the prompt
+// kernel; the G heads are the rows of one 16-row MMA tile (the other rows are zero). The four warps
+// split each 64-key tile into 16-key quarters, each with its own running softmax; their partial
+// results are merged through shared memory at the end. The new token's K/V rows are already in
+// the cache (kv_append_kernel).
+struct GqaAttnParams {
+  const float* q;  // [batch][q_stride], after RoPE
+  int q_stride;
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;
+  const float* v_scale;
+  const int* positions;  // [batch] position of the new token: keys 0..position are visible
+  const int* slots;      // [batch]
+  int nq, nkv, max_ctx;
+  float* out;  // [batch][out_stride]
+  int out_stride;
+  float att_scale;
+};
+
+template <bool KV_I8, int HD>
+__global__ void __launch_bounds__(PFA_THREADS, 3) attn_decode_gqa_kernel(const GqaAttnParams prm) {
+  static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+  constexpr int STR = pfa_stride(HD);
+  constexpr int KSTEPS = HD / 16;
+  constexpr int NT_O = HD / 8;
+  extern __shared__ __align__(16) unsigned char pfa_smem[];
+  __half* Ks = reinterpret_cast<__half*>(pfa_smem);
+  __half* Vs = Ks + PFA_K * STR;
+  float* ks_s = reinterpret_cast<float*>(Vs + PFA_K * STR);
+  float* vs_s = ks_s + PFA_K;
+  unsigned char* raw = reinterpret_cast<unsigned char*>(vs_s + PFA_K);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int G = prm.nq / prm.nkv;
+  const int pos = prm.positions[b];
+  const size_t crow0 = ((size_t)prm.slots[b] * prm.nkv + kvh) * prm.max_ctx;
+  const int kmax = pos;
+  const int nkt = kmax / PFA_K + 1;
+
+  // row g of the tile = query head kvh*G + g (g < G); rows G..15 are zero
+  uint32_t qa[KSTEPS][2];
+  {
+    const float* qr = prm.q + (size_t)b * prm.q_stride + (size_t)(kvh * G + min(g, G - 1)) * HD;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const float2 a = *reinterpret_cast<const float2*>(qr + ks * 16 + 2 * t);
+      const float2 c = *reinterpret_cast<const float2*>(qr + ks * 16 + 8 + 2 * t);
+      qa[ks][0] = g < G ? pfa_pack(a.x, a.y) : 0u;
+      qa[ks][1] = g < G ? pfa_pack(c.x, c.y) : 0u;
+    }
+  }
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, l0 = 0.f;
+  const float sc2 = prm.att_scale * 1.4426950408889634f;
+
+  auto fetch_scale = [&](int kt) -> float {
+    const int key = kt * PFA_K + (tid & 63);
+    if (key > kmax) return 0.f;
+    if (!KV_I8) return 1.f;
+    return (tid < 64 ? prm.k_scale : prm.v_scale)[crow0 + key];
+  };
+  constexpr int RAW_TILE = PFA_K * HD;
+  constexpr int CP_PER_THREAD = RAW_TILE / 16 / PFA_THREADS;
+  auto issue_raw = [&](int kt) {
+    unsigned char* dstk = raw + (size_t)(kt & 1) * 2 * RAW_TILE;
+    unsigned char* dstv = dstk + RAW_TILE;
+    const unsigned char* srck = reinterpret_cast<const unsigned char*>(prm.k_cache) + (crow0 + (size_t)kt * PFA_K) * HD;
+    const unsigned char* srcv = reinterpret_cast<const unsigned char*>(prm.v_cache) + (crow0 + (size_t)kt * PFA_K) * HD;
+#pragma unroll
+    for (int r = 0; r < CP_PER_THREAD; ++r) {
+      const int i = tid + r * PFA_THREADS;
+      const int key = kt * PFA_K + i / (HD / 16);
+      if (key <= kmax) {
+        pfa_cp16(dstk + (size_t)i * 16, srck + (size_t)i * 16);
+        pfa_cp16(dstv + (size_t)i * 16, srcv + (size_t)i * 16);
+      }
+    }
+  };
+
+  float sreg = 0.f;
+  if (KV_I8) issue_raw(0);
+  sreg = fetch_scale(0);
+  const int kw = 16 * warp;  // this warp's keys within a tile
+
+#pragma unroll 1
+  for (int kt = 0; kt < nkt; ++kt) {
+    if (KV_I8) pfa_cp_wait_all();
+    __syncthreads();
+    const float scur = sreg;
+    if (kt + 1 < nkt) {
+      if (KV_I8) issue_raw(kt + 1);
+      sreg = fetch_scale(kt + 1);
+    }
+    if (KV_I8) {
+      const unsigned char* srck = raw + (size_t)(kt & 1) * 2 * RAW_TILE;
+      const unsigned char* srcv = srck + RAW_TILE;
+#pragma unroll
+      for (int r = 0; r < CP_PER_THREAD; ++r) {
+        const int i = tid + r * PFA_THREADS;
+        const int key = i / (HD / 16), part = i % (HD / 16);
+        const uint4 wk = *reinterpret_cast<const uint4*>(srck + (size_t)i * 16);
+        const uint4 wv = *reinterpret_cast<const uint4*>(srcv + (size_t)i * 16);
+        uint4 a, c;
+        pfa_cvt4(wk.x, a.x, a.y); pfa_cvt4(wk.y, a.z, a.w); pfa_cvt4(wk.z, c.x, c.y); pfa_cvt4(wk.w, c.z, c.w);
+        uint4* dk = reinterpret_cast<uint4*>(Ks + key * STR + part * 16);
+        dk[0] = a; dk[1] = c;
+        pfa_cvt4(wv.x, a.x, a.y); pfa_cvt4(wv.y, a.z, a.w); pfa_cvt4(wv.z, c.x, c.y); pfa_cvt4(wv.w, c.z, c.w);
+        uint4* dv = reinterpret_cast<uint4*>(Vs + key * STR + part * 16);
+        dv[0] = a; dv[1] = c;
+      }
+    } else {
+      const float* srck = reinterpret_cast<const float*>(prm.k_cache) + (crow0 + (size_t)kt * PFA_K) * HD;
+      const float* srcv = reinterpret_cast<const float*>(prm.v_cache) + (crow0 + (size_t)kt * PFA_K) * HD;
+      constexpr int F4 = PFA_K * HD / 4 / PFA_THREADS;
+#pragma unroll 4
+      for (int r = 0; r < F4; ++r) {
+        const int i = tid + r * PFA_THREADS;
+        const int key = i / (HD / 4), part = i % (HD / 4);
+        float4 fk = make_float4(0.f, 0.f, 0.f, 0.f), fv = fk;
+        if (kt * PFA_K + key <= kmax) {
+          fk = *reinterpret_cast<const float4*>(srck + (size_t)i * 4);
+          fv = *reinterpret_cast<const float4*>(srcv + (size_t)i * 4);
+        }
+        *reinterpret_cast<uint2*>(Ks + key * STR + part * 4) = make_uint2(pfa_pack(fk.x, fk.y), pfa_pack(fk.z, fk.w));
+        *reinterpret_cast<uint2*>(Vs + key * STR + part * 4) = make_uint2(pfa_pack(fv.x, fv.y), pfa_pack(fv.z, fv.w));
+      }
+    }
+    (tid < 64 ? ks_s : vs_s)[tid & 63] = scur;
+    __syncthreads();
+    if (kt * PFA_K + kw > kmax) continue;  // this warp's quarter of the tile lies past the newest key (uniform per warp)
+
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks += 2) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        uint32_t bf[4];
+        pfa_ldm4(bf, Ks + (kw + nt * 8 + (lane & 7)) * STR + ks * 16 + (lane >> 3) * 8);
+        pfa_mma(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, bf[0], bf[1]);
+        pfa_mma(s[nt], qa[ks + 1][0], 0u, qa[ks + 1][1], 0u, bf[2], bf[3]);
+      }
+    }
+    const int kbase = kt * PFA_K + kw + 2 * t;
+    float mx0 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float2 kk = *reinterpret_cast<const float2*>(ks_s + kw + nt * 8 + 2 * t);
+      const int key = kbase + nt * 8;
+      s[nt][0] = key <= pos ? s[nt][0] * (kk.x * sc2) : -INFINITY;
+      s[nt][1] = key + 1 <= pos ? s[nt][1] * (kk.y * sc2) : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    const float mn0 = fmaxf(m0, mx0);  // finite: the quarter's first key is visible (checked above)
+    const float al0 = exp2f(m0 - mn0);
+    m0 = mn0;
+    uint32_t pa[2];
+    float ls0 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float2 vv = *reinterpret_cast<const float2*>(vs_s + kw + nt * 8 + 2 * t);
+      const float p0 = exp2f(s[nt][0] - mn0), p1 = exp2f(s[nt][1] - mn0);
+      ls0 += p0 + p1;
+      pa[nt] = pfa_pack(p0 * vv.x, p1 * vv.y);
+    }
+    l0 = l0 * al0 + ls0;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) { o[i][0] *= al0; o[i][1] *= al0; }
+#pragma unroll
+    for (int np = 0; np < HD / 16; ++np) {
+      uint32_t bf[4];
+      pfa_ldm4t(bf, Vs + (kw + (lane & 7) + ((lane >> 3) & 1) * 8) * STR + np * 16 + (lane >> 4) * 8);
+      pfa_mma(o[2 * np], pa[0], 0u, pa[1], 0u, bf[0], bf[1]);
+      pfa_mma(o[2 * np + 1], pa[0], 0u, pa[1], 0u, bf[2], bf[3]);
+    }
+  }
+
+  // ---- merge the four warps' partial results: [warp][G][HD] outputs and [warp][G] (max, sum) pairs ----
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  __syncthreads();  // everybody is done with the K/V tiles
+  float* po = reinterpret_cast<float*>(pfa_smem);                 // [4][8][HD]
+  float* pml = po + 4 * 8 * HD;                                   // [4][8][2]
+  if (g < G) {
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + ((size_t)warp * 8 + g) * HD + i * 8 + 2 * t) = make_float2(o[i][0], o[i][1]);
+    if (t == 0) { pml[(warp * 8 + g) * 2] = m0; pml[(warp * 8 + g) * 2 + 1] = l0; }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * HD; idx += PFA_THREADS) {
+    const int gq = idx / HD, d = idx - gq * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, pml[(w * 8 + gq) * 2]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = pml[(w * 8 + gq) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);  // a warp that saw no key contributes nothing
+      L += pml[(w * 8 + gq) * 2 + 1] * f;
+      O += po[((size_t)w * 8 + gq) * HD + d] * f;
+    }
+    prm.out[(size_t)b * prm.out_stride + (size_t)(kvh * G + gq) * HD + d] = O / (L + 1e-9f);
+  }
+}
+
 }  // namespace b200

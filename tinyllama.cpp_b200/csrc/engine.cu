@@ -61,6 +61,10 @@ static void set_gemv_attrs() {
   CK(cudaFuncSetAttribute((attn_prefill_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 128)));
   CK(cudaFuncSetAttribute((attn_prefill_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 64)));
   CK(cudaFuncSetAttribute((attn_prefill_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 128)));
+  CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<true, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 64)));
+  CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 128)));
+  CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 64)));
+  CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 128)));
   done = true;
 }
 
@@ -82,6 +86,28 @@ static void launch_prefill_attention(const PrefillAttnParams& a, bool kv_i8, int
     else attn_prefill_kernel<false, 64><<<grid, PFA_THREADS, smem, st>>>(a);
   } else {
     throw std::runtime_error("prompt attention kernel: head_dim must be 64 or 128");
+  }
+  CK(cudaGetLastError());
+}
+
+// Batched decode of grouped-query models: one CTA per (sequence, KV head) on the tensor cores.
+// B200_GQA_ATTN=0 keeps the per-head decode kernel, =2 also uses this kernel when every query head
+// has its own KV head.
+static bool gqa_attn_available(int hd, int nq, int nkv) {
+  static const int mode = [] { const char* v = std::getenv("B200_GQA_ATTN"); return v ? atoi(v) : 1; }();
+  const int G = nq / nkv;
+  return mode != 0 && (hd == 64 || hd == 128) && G <= 8 && (G >= 2 || mode == 2);
+}
+
+static void launch_gqa_attention(const GqaAttnParams& a, int batch, bool kv_i8, int hd, cudaStream_t st) {
+  const dim3 grid(a.nkv, batch);
+  const size_t smem = pfa_smem_bytes(kv_i8, hd);
+  if (hd == 128) {
+    if (kv_i8) attn_decode_gqa_kernel<true, 128><<<grid, PFA_THREADS, smem, st>>>(a);
+    else attn_decode_gqa_kernel<false, 128><<<grid, PFA_THREADS, smem, st>>>(a);
+  } else {
+    if (kv_i8) attn_decode_gqa_kernel<true, 64><<<grid, PFA_THREADS, smem, st>>>(a);
+    else attn_decode_gqa_kernel<false, 64><<<grid, PFA_THREADS, smem, st>>>(a);
   }
   CK(cudaGetLastError());
 }
@@ -458,7 +484,20 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.trace = trace_rec(e, launches);
       launches += launch_linear(e, p, batch, st, use_tc);
     }
-    {
+    if (use_tc && gqa_attn_available(e->hd, e->nq, e->nkv)) {
+      const bool i8 = e->desc.kv_dtype == B200_KV_I8;
+      kv_append_kernel<<<dim3(batch, (e->nkv + KVA_WARPS - 1) / KVA_WARPS, 2), 32 * KVA_WARPS, 0, st>>>(e->d_kvnew, 2 * KVD, e->d_positions, e->d_slots, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0,
+                                                             w.k_cache, w.v_cache, w.k_scale, w.v_scale);
+      CK(cudaGetLastError());
+      GqaAttnParams a{};
+      a.q = e->d_q; a.q_stride = e->Hq;
+      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+      a.positions = e->d_positions; a.slots = e->d_slots;
+      a.nq = e->nq; a.nkv = e->nkv; a.max_ctx = e->max_ctx;
+      a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      launch_gqa_attention(a, batch, i8, e->hd, st);
+      launches += 2;
+    } else {
       AttnParams a{};
       a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
       a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
@@ -587,7 +626,7 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
       p.rope = e->rope; p.positions = d_pos; p.head_dim = e->hd; p.max_pos = e->desc.max_position_embeddings;
       launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
     }
-    kv_append_kernel<<<dim3(T, e->nkv, 2), 32, 0, st>>>(e->pf_kvnew, 2 * KVD, d_pos, d_slot, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0, w.k_cache,
+    kv_append_kernel<<<dim3(T, (e->nkv + KVA_WARPS - 1) / KVA_WARPS, 2), 32 * KVA_WARPS, 0, st>>>(e->pf_kvnew, 2 * KVD, d_pos, d_slot, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0, w.k_cache,
                                                         w.v_cache, w.k_scale, w.v_scale);
     CK(cudaGetLastError());
     if (prefill_attn_available(e->hd)) {
