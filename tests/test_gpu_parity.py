@@ -295,14 +295,16 @@ def test_batch16_decode_takes_tensor_core_path(pkg, tiny_models, scheme, kv):
     eng.close()
 
 
+@pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("kv", ["f32", "i8"])
-def test_batch_decode_grouped_query_attention_long_contexts(pkg, tiny_models, kv):
+def test_batch_decode_grouped_query_attention_long_contexts(pkg, tiny_models, kv, splits, monkeypatch):
     """Batched decode of a grouped-query model (2 query heads per KV head) with ragged contexts of up to two
     64-key tiles: the tensor-core attention that serves a whole group per CTA, all four key quarters and the
     merge of their partial softmaxes. Logits against the oracle: 2e-2 absolute (FP32 cache); with the INT8
     cache the prompt's K/V rows come from fp16 matmuls and may round to a neighbouring int8 step, so the
     bound is relative to the largest logit as in the prompt tests."""
     B = 16
+    monkeypatch.setenv("B200_GQA_SPLITS", str(splits))  # context runs per sequence (3: with empty runs and the cross-CTA merge)
     kvd = pkg.KV_I8 if kv == "i8" else pkg.KV_F32
     eng = pkg.Engine.from_gguf(tiny_models[1], max_seqs=B, kv_dtype=kvd)
     orc = ol.OracleModel.from_gguf(tiny_models[1], max_seqs=B, kv_int8=(kv == "i8"))

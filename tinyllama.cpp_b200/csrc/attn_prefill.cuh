@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "attn.cuh"
+
 namespace b200 {
 
 struct PrefillAttnParams {
@@ -286,7 +288,10 @@ __global__ void __launch_bounds__(PFA_THREADS, 2) attn_prefill_kernel(const Pref
 // kernel; the G heads are the rows of one 16-row MMA tile (the other rows are zero). The four warps
 // split each 64-key tile into 16-key quarters, each with its own running softmax; their partial
 // results are merged through shared memory at the end. The new token's K/V rows are already in
-// the cache (kv_append_kernel).
+// the cache (kv_append_kernel). With nsplit > 1 the context of every sequence is cut into nsplit
+// runs of whole tiles, one CTA each (grid.z): a CTA then writes its (max, sum, weighted V) partials in
+// the decode kernel's format and the last CTA of the (sequence, KV head) to finish merges them
+// (ticket, attn_merge_head), so that one long sequence does not hold a layer's attention back.
 struct GqaAttnParams {
   const float* q;  // [batch][q_stride], after RoPE
   int q_stride;
@@ -300,6 +305,10 @@ struct GqaAttnParams {
   float* out;  // [batch][out_stride]
   int out_stride;
   float att_scale;
+  int nsplit;      // context runs per sequence (<= ATTN_MAX_SPLITS)
+  float* part_o;   // [batch][nq][nsplit][hd]   (nsplit > 1)
+  float* part_ml;  // [batch][nq][nsplit][2]
+  int* tickets;    // [batch][nq], zero between launches; entry of the group's first head is used
 };
 
 template <bool KV_I8, int HD>
@@ -321,7 +330,10 @@ __global__ void __launch_bounds__(PFA_THREADS, 3) attn_decode_gqa_kernel(const G
   const int pos = prm.positions[b];
   const size_t crow0 = ((size_t)prm.slots[b] * prm.nkv + kvh) * prm.max_ctx;
   const int kmax = pos;
-  const int nkt = kmax / PFA_K + 1;
+  const int nkt_all = kmax / PFA_K + 1;
+  const int split = blockIdx.z;
+  const int tiles_per_split = (nkt_all + prm.nsplit - 1) / prm.nsplit;
+  const int kt0 = split * tiles_per_split, nkt = min(nkt_all, kt0 + tiles_per_split);  // this CTA's tiles: kt0 .. nkt-1 (possibly none)
 
   // row g of the tile = query head kvh*G + g (g < G); rows G..15 are zero
   uint32_t qa[KSTEPS][2];
@@ -366,12 +378,14 @@ __global__ void __launch_bounds__(PFA_THREADS, 3) attn_decode_gqa_kernel(const G
   };
 
   float sreg = 0.f;
-  if (KV_I8) issue_raw(0);
-  sreg = fetch_scale(0);
+  if (kt0 < nkt) {
+    if (KV_I8) issue_raw(kt0);
+    sreg = fetch_scale(kt0);
+  }
   const int kw = 16 * warp;  // this warp's keys within a tile
 
 #pragma unroll 1
-  for (int kt = 0; kt < nkt; ++kt) {
+  for (int kt = kt0; kt < nkt; ++kt) {
     if (KV_I8) pfa_cp_wait_all();
     __syncthreads();
     const float scur = sreg;
@@ -491,8 +505,38 @@ __global__ void __launch_bounds__(PFA_THREADS, 3) attn_decode_gqa_kernel(const G
       L += pml[(w * 8 + gq) * 2 + 1] * f;
       O += po[((size_t)w * 8 + gq) * HD + d] * f;
     }
-    prm.out[(size_t)b * prm.out_stride + (size_t)(kvh * G + gq) * HD + d] = O / (L + 1e-9f);
+    const int h = kvh * G + gq;
+    if (prm.nsplit == 1) {
+      prm.out[(size_t)b * prm.out_stride + (size_t)h * HD + d] = O / (L + 1e-9f);
+    } else {  // partials as the decode kernel writes them: maximum in natural-log units, sum and weighted V relative to it
+      const size_t pi = ((size_t)b * prm.nq + h) * prm.nsplit + split;
+      prm.part_o[pi * HD + d] = O;
+      if (d == 0) {
+        prm.part_ml[pi * 2] = M * 0.6931471805599453f;
+        prm.part_ml[pi * 2 + 1] = L;
+      }
+    }
   }
+  if (prm.nsplit == 1) return;
+  __shared__ int last_flag;
+  __syncthreads();  // every thread's partials are written; one thread publishes them for the whole CTA
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(&prm.tickets[b * prm.nq + kvh * G], 1);
+    last_flag = (old == prm.nsplit - 1);
+    if (last_flag) __threadfence();
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  AttnParams ap{};
+  ap.nq = prm.nq; ap.hd = HD; ap.nsplit = prm.nsplit; ap.part_o = prm.part_o; ap.part_ml = prm.part_ml;
+  float* scratch = reinterpret_cast<float*>(pfa_smem);
+  for (int gq = 0; gq < G; ++gq) {
+    const int h = kvh * G + gq;
+    attn_merge_head(ap, b, h, tid, PFA_THREADS, prm.out + (size_t)b * prm.out_stride + (size_t)h * HD, scratch, 1);
+    group_sync(1);  // the scratch is reused by the next head
+  }
+  if (tid == 0) prm.tickets[b * prm.nq + kvh * G] = 0;
 }
 
 }  // namespace b200

@@ -99,8 +99,15 @@ static bool gqa_attn_available(int hd, int nq, int nkv) {
   return mode != 0 && (hd == 64 || hd == 128) && G <= 8 && (G >= 2 || mode == 2);
 }
 
+// Context runs per sequence for the grouped-query batch attention: about 1024 keys per CTA at the
+// engine's maximum context (B200_GQA_SPLITS overrides), at most 8.
+static int gqa_attn_splits(const b200_engine* e) {
+  if (const char* v = std::getenv("B200_GQA_SPLITS")) return std::max(1, std::min(atoi(v), 8));
+  return std::max(1, std::min((e->max_ctx + 1023) / 1024, 8));
+}
+
 static void launch_gqa_attention(const GqaAttnParams& a, int batch, bool kv_i8, int hd, cudaStream_t st) {
-  const dim3 grid(a.nkv, batch);
+  const dim3 grid(a.nkv, batch, a.nsplit);
   const size_t smem = pfa_smem_bytes(kv_i8, hd);
   if (hd == 128) {
     if (kv_i8) attn_decode_gqa_kernel<true, 128><<<grid, PFA_THREADS, smem, st>>>(a);
@@ -495,6 +502,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       a.positions = e->d_positions; a.slots = e->d_slots;
       a.nq = e->nq; a.nkv = e->nkv; a.max_ctx = e->max_ctx;
       a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      a.nsplit = gqa_attn_splits(e); a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
       launch_gqa_attention(a, batch, i8, e->hd, st);
       launches += 2;
     } else {
