@@ -417,7 +417,8 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
     t.epi = EPI_STORE; t.y = e->d_tc_part; t.y_stride = p.seg[0].rows;
     launch_gemm_tc(e, t, st);
     const size_t nel = (size_t)batch * p.seg[0].rows;
-    splitk_reduce_kernel<<<(unsigned)std::min<size_t>((nel + 255) / 256, 1184), 256, 0, st>>>(e->d_tc_part, t.ksplit, batch, p.seg[0].rows, p.resid, p.y, p.y_stride);
+    if (p.seg[0].rows % 4 || p.y_stride % 4) throw std::runtime_error("split-K matmul: rows must be a multiple of 4");
+    splitk_reduce_kernel<<<(unsigned)std::min<size_t>((nel / 4 + 255) / 256, 1184), 256, 0, st>>>(e->d_tc_part, t.ksplit, batch, p.seg[0].rows, p.resid, p.y, p.y_stride);
     CK(cudaGetLastError());
     ++n;
   } else {

@@ -503,14 +503,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
 }
 
 // Split-K epilogue: y[t][r] = (resid ? resid : y)[t][r] + sum_z part[z][t][r], z in order (deterministic).
+// Four consecutive rows per thread (the launcher checks that rows and y_stride are multiples of 4).
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int ksplit, int T, int rows, const float* __restrict__ resid,
                                      float* __restrict__ y, int y_stride) {
-  const size_t n = (size_t)T * rows;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = i / rows, r = i - t * rows;
-    float acc = (resid ? resid : y)[t * y_stride + r];
-    for (int z = 0; z < ksplit; ++z) acc += part[(size_t)z * n + i];
-    y[t * y_stride + r] = acc;
+  const size_t n = (size_t)T * rows, n4 = n / 4;
+  const int rows4 = rows / 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / rows4, r = (i - t * rows4) * 4;
+    float4 acc = *reinterpret_cast<const float4*>((resid ? resid : y) + t * y_stride + r);
+    for (int z = 0; z < ksplit; ++z) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(part + (size_t)z * n) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(y + t * y_stride + r) = acc;
   }
 }
 
