@@ -224,9 +224,11 @@ __device__ __forceinline__ void tc_dequant16(int type, const TcRaw& t, int kc, i
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t lword = u4_word(t.r[hh], i), hword = u4_word(t.r[2 + hh], i);
-      const uint32_t nib = ((j >> 1) ? (lword >> 4) : lword) & 0x0F0F0F0Fu;
-      const uint32_t top = (j == 0 ? (hword << 4) : j == 1 ? (hword << 2) : j == 2 ? hword : (hword >> 2)) & 0x30303030u;
-      const uint32_t six = nib | top | 0x80808080u;
+      // low nibbles from ql (its high nibbles for q3 / q4), bits 4-5 from the qh pair of this quarter: one variable
+      // shift brings that pair to bits 4-5, one bitwise select joins the two, one more clears bits 6-7 and sets bit 7
+      const uint32_t lo = (kc & 1) ? (lword >> 4) : lword;
+      const uint32_t hi = (kc & 1) ? (hword >> (2 * half)) : (hword << (4 - 2 * half));
+      const uint32_t six = (((lo ^ hi) & 0x0F0F0F0Fu) ^ hi) & 0x3F3F3F3Fu | 0x80808080u;
 #pragma unroll
       for (int k = 0; k < 4; ++k) v[4 * i + k] = fmaf(S, byte_to_unit_float(six, k), C);  // sc * (q - 32)
     }
