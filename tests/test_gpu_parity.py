@@ -85,7 +85,8 @@ def test_matvec_many_tiles_per_cta(pkg, name, rows, cols):
 
 @pytest.mark.parametrize("name,rows,cols,tokens", [("q4_k", 128, 256, 16), ("q8_0", 64, 256, 16), ("q6_k", 130, 512, 32),
                                                    ("q4_k", 1024, 4096, 64), ("q6_k", 512, 11008, 48), ("q4_k", 300, 1024, 300),
-                                                   ("q8_0", 520, 2048, 17), ("q4_k", 18944, 4096, 256)])
+                                                   ("q8_0", 520, 2048, 17), ("q4_k", 18944, 4096, 256), ("q4_k", 1024, 4096, 512),
+                                                   ("q6_k", 512, 1024, 400)])
 def test_matmul_tensor_core(pkg, name, rows, cols, tokens):
     """The tcgen05 / TMEM matmul (batch >= 16 and prompt path) against the FP64 product of the dequantised
     weights. Operands are rounded to fp16, so the tolerance is 2e-3 of the largest output (measured 3e-4)."""

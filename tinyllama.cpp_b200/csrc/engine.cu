@@ -239,8 +239,16 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   set_gemv_attrs();
   const GemvGeom g0 = gemv_geometry(p.seg[0].type, p.K);
   p.nblk = g0.nblk; p.nslab = g0.nslab; p.S = g0.S; p.S_last = g0.S_last; p.R = g0.R;
-  int NT = (p.T + 31) / 32 * 32;  // token tile: the whole batch when it fits, else tiles of 256
-  if (NT > TC_MAX_N) NT = TC_MAX_N;
+  int ub_max0 = 0;
+  for (int s = 0; s < p.nseg; ++s) ub_max0 = std::max(ub_max0, gemv_unit_bytes(p.seg[s].type));
+  // token tile: the whole batch when it fits (two MMA halves above 256 tokens: the tile then needs a multiple of 64,
+  // and its 64 KB activation stages leave room for one stage of packed units only if those are Q4_K), else tiles of 256
+  int NT = (p.T + 31) / 32 * 32;
+  if (NT > 256) {
+    NT = (p.T + 63) / 64 * 64;
+    if (NT > TC_MAX_N) NT = TC_MAX_N;
+    if (tc_smem_bytes(NT, 4, 2, 1, (TC_M * ub_max0 + 127) / 128 * 128) > (size_t)TC_SMEM_MAX) NT = 256;
+  }
   p.NT = NT;
   p.tmem_cols = 32;
   while (p.tmem_cols < NT) p.tmem_cols *= 2;
@@ -258,9 +266,9 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   static const int a_force = [] { const char* v = std::getenv("B200_TC_A_STAGES"); return v ? atoi(v) : 0; }();
   p.a_stages = NT <= 128 ? 8 : 4;
   if (a_force == 4 || a_force == 8) p.a_stages = a_force;
-  p.b_stages = NT > 128 ? 3 : 4;
+  p.b_stages = NT > 256 ? 2 : NT > 128 ? 3 : 4;
   auto fits = [&](int w) { return tc_smem_bytes(NT, p.a_stages, p.b_stages, w, p.w_stage_bytes) <= (size_t)TC_SMEM_MAX; };
-  if (p.a_stages == 8 && !fits(2)) { p.b_stages = 2; if (!fits(1)) { p.a_stages = 4; p.b_stages = NT > 128 ? 3 : 4; } }
+  if (p.a_stages == 8 && !fits(2)) { p.b_stages = 2; if (!fits(1)) { p.a_stages = 4; p.b_stages = NT > 256 ? 2 : NT > 128 ? 3 : 4; } }
   p.w_stages = TC_W_STAGES;
   while (p.w_stages > 1 && !fits(p.w_stages)) --p.w_stages;
   if (!fits(p.w_stages)) throw std::runtime_error("tensor-core matmul: tile does not fit shared memory");
@@ -272,7 +280,7 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   {  // activation tiles: 64 elements along K x NT tokens, written in the 128-byte-swizzle layout; tokens beyond T read as zero
     const cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
     const cuuint64_t gstr[1] = {(cuuint64_t)p.K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)NT};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)(NT > 256 ? NT / 2 : NT)};
     encode_map(&maps.act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.x16, gdim, gstr, box, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   if (!p.w_rowcopy) {
@@ -410,7 +418,7 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
   const int ctas = (int)((p.seg[0].rows + TC_M - 1) / TC_M) * ((batch + TC_MAX_N - 1) / TC_MAX_N);
   const int nblk = p.K / 256;
   int ks = 1;
-  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 256 && e->d_tc_part) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
+  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 512 && e->d_tc_part) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
   if (ks > 1) {
     t.ksplit = ks; t.kblocks = (nblk + ks - 1) / ks;
     t.ksplit = (nblk + t.kblocks - 1) / t.kblocks;  // no empty split
@@ -586,7 +594,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
 // K/V rows are appended to the cache first, then every token runs the decode-attention kernel over
 // the cache rows up to and including its own position (causal). Only the last token's logits are
 // computed (the reference computes all rows and keeps the last, model.cpp:1094-1156).
-constexpr int PF_CHUNK = 256;
+constexpr int PF_CHUNK = 512;
 
 static void ensure_prefill_buffers(b200_engine* e) {
   if (e->pf_cap) return;

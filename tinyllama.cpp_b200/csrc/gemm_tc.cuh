@@ -39,7 +39,7 @@ constexpr int TC_M = 128;        // weight rows per CTA tile (the MMA's M)
 constexpr int TC_KC = 64;        // elements along K per shared-memory stage: one 128-byte swizzled row of fp16
 constexpr int TC_WORKERS = 512;   // sixteen dequantising warps: thread = (weight row, 16-element quarter of the 64-element step)
 constexpr int TC_THREADS = TC_WORKERS + 96;  // + the MMA warp, the weight-producer warp and the activation-producer warp
-constexpr int TC_MAX_N = 256;     // tokens per CTA tile
+constexpr int TC_MAX_N = 512;     // tokens per CTA tile (all 512 TMEM columns); above 256 the tile is two MMA halves
 
 struct TcParams {
   GemvSeg seg[3];
@@ -48,7 +48,7 @@ struct TcParams {
   int nblk, nslab, S, S_last, R;  // GemvGeom of K (where a unit sits inside the stage images)
   const __half* x16;              // [T][K] activations (already normalised when the layer asks for it)
   int T;                          // tokens
-  int NT;                         // tokens per CTA tile: a multiple of 16, <= 256
+  int NT;                         // tokens per CTA tile: a multiple of 32, <= 512 (a multiple of 64 above 256)
   int tmem_cols;                  // power of two >= max(32, NT)
   int epi;                        // EPI_STORE / EPI_RESID / EPI_QKV_ROPE / EPI_SWIGLU
   float* y;                       // [T][y_stride]
@@ -341,7 +341,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
     //      instruction waits for the one before), so it is kept to the bare minimum: running stage
     //      counters instead of divisions, descriptors advanced by constants, loads left to others ----
     if (lane == 0) {
-      const uint32_t idesc = tc_idesc(p.NT);
+      const int nhalf = p.NT > 256 ? 2 : 1, nmma = p.NT / nhalf;  // one MMA covers at most 256 tokens
+      const uint32_t idesc = tc_idesc(nmma);
+      const uint64_t b_half = (uint64_t)((nmma * 128) >> 4);  // descriptor units between the two token halves of an activation stage
       const int nb = p.b_stages, na = p.a_stages;
       const uint64_t adesc0 = tc_smem_desc(smem_u32(Abase)), bdesc0 = tc_smem_desc(smem_u32(Bbase));
       const uint64_t a_step = (uint64_t)((TC_M * 128) >> 4), b_step = (uint64_t)(b_stage_bytes >> 4);
@@ -355,7 +357,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (s | k4) ? 1u : 0u);  // 16 elements along K = 32 bytes = 2 descriptor units
+        for (int k4 = 0; k4 < 4; ++k4) {  // 16 elements along K = 32 bytes = 2 descriptor units
+          tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (s | k4) ? 1u : 0u);
+          if (nhalf == 2) tc_mma_f16(tmem_d + (uint32_t)nmma, adesc + 2 * k4, bdesc + b_half + 2 * k4, idesc, (s | k4) ? 1u : 0u);
+        }
         tc_commit(&sh.mma_done[sa]);
         adesc += a_step; bdesc += b_step;
         if (++sa == na) { sa = 0; pa ^= 1u; adesc = adesc0; }
@@ -374,7 +379,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         if (s >= nb) tc_wait(p, &sh, &sh.mma_done[(s - nb) % na], (uint32_t)(((s - nb) / na) & 1));
         void* bar = &sh.b_full[s % nb];
         mbar_expect_tx(bar, b_stage_bytes);
-        tc_tma_load_2d(Bbase + (size_t)(s % nb) * b_stage_bytes, &maps.act, (4 * blk0 + s) * TC_KC, t0, bar);
+        uint8_t* dst = Bbase + (size_t)(s % nb) * b_stage_bytes;
+        tc_tma_load_2d(dst, &maps.act, (4 * blk0 + s) * TC_KC, t0, bar);
+        if (p.NT > 256) tc_tma_load_2d(dst + (size_t)(p.NT / 2) * 128, &maps.act, (4 * blk0 + s) * TC_KC, t0 + p.NT / 2, bar);  // a box holds at most 256 rows
       }
     }
     __syncwarp();
