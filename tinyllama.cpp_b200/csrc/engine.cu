@@ -247,7 +247,7 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   if (NT > 256) {
     NT = (p.T + 63) / 64 * 64;
     if (NT > TC_MAX_N) NT = TC_MAX_N;
-    if (tc_smem_bytes(NT, 4, 2, 1, (TC_M * ub_max0 + 127) / 128 * 128) > (size_t)TC_SMEM_MAX) NT = 256;
+    if (tc_smem_bytes(NT, 4, 2, 1, (TC_M * ub_max0 + 127) / 128 * 128, p.nslab) > (size_t)TC_SMEM_MAX) NT = 256;
   }
   p.NT = NT;
   p.tmem_cols = 32;
@@ -267,7 +267,7 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
   p.a_stages = NT <= 128 ? 8 : 4;
   if (a_force == 4 || a_force == 8) p.a_stages = a_force;
   p.b_stages = NT > 256 ? 2 : NT > 128 ? 3 : 4;
-  auto fits = [&](int w) { return tc_smem_bytes(NT, p.a_stages, p.b_stages, w, p.w_stage_bytes) <= (size_t)TC_SMEM_MAX; };
+  auto fits = [&](int w) { return tc_smem_bytes(NT, p.a_stages, p.b_stages, w, p.w_stage_bytes, p.nslab) <= (size_t)TC_SMEM_MAX; };
   if (p.a_stages == 8 && !fits(2)) { p.b_stages = 2; if (!fits(1)) { p.a_stages = 4; p.b_stages = NT > 256 ? 2 : NT > 128 ? 3 : 4; } }
   p.w_stages = TC_W_STAGES;
   while (p.w_stages > 1 && !fits(p.w_stages)) --p.w_stages;
@@ -300,7 +300,7 @@ static void launch_gemm_tc(const b200_engine* e, TcParams p, cudaStream_t st) {
     }
   }
   dim3 grid(p.ntiles_m, (p.T + NT - 1) / NT, p.ksplit);
-  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT, p.a_stages, p.b_stages, p.w_stages, p.w_stage_bytes), st>>>(p, maps);
+  gemm_tc_kernel<<<grid, TC_THREADS, tc_smem_bytes(NT, p.a_stages, p.b_stages, p.w_stages, p.w_stage_bytes, p.nslab), st>>>(p, maps);
   CK(cudaGetLastError());
 }
 

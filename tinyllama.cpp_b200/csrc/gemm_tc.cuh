@@ -291,8 +291,9 @@ __device__ __forceinline__ void tc_tma_load_2d(void* dst, const void* tmap, int 
 // moves the packed weights, warp 18 the activation tiles. Dynamic shared memory (1024-byte aligned):
 // 4 or 8 weight stages of 16 KB, 2-4 activation stages of NT x 128 bytes, the packed-weight ring,
 // the Q6_K scale buffers.
-__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT, int a_stages, int b_stages, int w_stages, int w_stage_bytes) {
-  return 1024 + a_stages * (size_t)TC_M * 128 + b_stages * (size_t)NT * 128 + (size_t)w_stages * w_stage_bytes + TC_D_BYTES;
+// nslab: slabs per stage-image tile; rows that are one slab long need one Q6_K scale buffer, not two
+__host__ __device__ __forceinline__ size_t tc_smem_bytes(int NT, int a_stages, int b_stages, int w_stages, int w_stage_bytes, int nslab) {
+  return 1024 + a_stages * (size_t)TC_M * 128 + b_stages * (size_t)NT * 128 + (size_t)w_stages * w_stage_bytes + (nslab == 1 ? TC_D_BYTES / 2 : TC_D_BYTES);
 }
 constexpr int TC_SMEM_MAX = 226 * 1024;  // dynamic part; the barriers live in static shared memory
 
