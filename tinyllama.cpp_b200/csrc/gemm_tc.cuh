@@ -2,7 +2,8 @@
 //   Y[t][row] = sum_k W[row][k] * X[t][k]        (W packed Q8_0 / Q4_K / Q6_K, X fp16, fp32 accumulate)
 // Replaces matmul_*_f32_batch_cpu (reference utils.cpp:730-782, 890-1044) / smart_gemm_batch_cuda
 // (model.cpp:2141-2249). "Swap-AB": the weight rows are the M side of the MMA (128 per CTA tile),
-// the tokens the N side (16..256 per tile).
+// the tokens the N side (32..512 per tile; above 256 a K step issues two 256-token MMA halves that
+// share the dequantised weight stage, so the accumulator fills all 512 tensor-memory columns).
 //
 // A CTA (608 threads) owns one tile of 128 rows x NT tokens and walks K in steps of 64 elements.
 // Five roles meet only on mbarriers; there is no block-wide barrier inside the K loop:
