@@ -591,8 +591,9 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
 // forward_device_batch_prefill (reference model.cpp:1526-1862) / CPUBatchProcessor::forward_cpu_batch
 // (cpu_batch_processor.cpp:11-281): all tokens of a chunk go through every layer together. Linear
 // layers = fp16 conversion (+RMSNorm, batch form: eps as configured) + tcgen05 matmul; the chunk's
-// K/V rows are appended to the cache first, then every token runs the decode-attention kernel over
-// the cache rows up to and including its own position (causal). Only the last token's logits are
+// K/V rows are appended to the cache first, then the prompt-attention kernel (64 queries per CTA on
+// the fp16 tensor cores; head sizes other than 64 / 128: the decode-attention kernel per token) runs
+// over the cache rows up to and including each token's own position (causal). Only the last token's logits are
 // computed (the reference computes all rows and keeps the last, model.cpp:1094-1156).
 constexpr int PF_CHUNK = 512;
 

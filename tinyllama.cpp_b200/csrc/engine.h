@@ -99,7 +99,7 @@ struct b200_engine {
   float* pf_part_o = nullptr;
   float* pf_part_ml = nullptr;
   int* pf_tickets = nullptr;
-  float* d_tc_part = nullptr;   // split-K partial outputs of the tensor-core matmul, [8][PF_CHUNK][H], allocated at first use
+  float* d_tc_part = nullptr;   // split-K partial outputs of the tensor-core matmul, [8][512][H], allocated when the engine is finalized
   int gemm_min_batch = 16;      // batches at least this large take the tensor-core matmul (B200_GEMM_MIN_BATCH)
   float* d_logits = nullptr;
   float* d_amax_val = nullptr;
