@@ -31,8 +31,14 @@ WORKLOADS = {
     "c3-llama2-7b-q4km-bs16": ("llama2-7b", 1, 16, 1024, "i8"),
     # ragged contexts: prompt lengths uniform in [256, 4096] from PCG64(99)
     "c4-llama3-8b-q6k-bs64": ("llama3-8b", 2, 64, (256, 4096), "i8"),
+    # 70B shape: the reference caps the context at 8192 positions (model_config.cpp:171-177), so the
+    # "8192-token context + 128 steps" of the configuration is run as an 8064-token prompt + 128 steps
+    "c5-llama2-70b-q4km-bs1": ("llama2-70b", 1, 1, 8064, "i8"),
+    "c5-llama2-70b-q4km-bs32": ("llama2-70b", 1, 32, 8064, "i8"),
     "tiny": ("tiny", 1, 1, 16, "i8"),
 }
+# golden case of tests/golden/full_models.npz that belongs to a (shape, scheme): used by the in-run parity check
+GOLDEN_CASE = {("tinyllama-1.1b", 0): "c1", ("tinyllama-1.1b", 1): "c2", ("llama2-7b", 1): "c3"}
 DEFAULT_WORKLOAD = "c3-llama2-7b-q4km-bs1"
 METRIC = "decode tokens/s (Llama-2-7B Q4_K_M, bs=1) and % of HBM roofline at 1/2/4/8 B200"
 
@@ -106,39 +112,86 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-def cpu_reference_tokens_per_s(path, budget_s, max_tokens):
-    """Times the reference's own CPU forward (oracle/_ref) on the same model file: decode steps from
-    an empty context, as many as fit the time budget (at least one)."""
+def cpu_reference_tokens_per_s(path, budget_s, max_tokens, prompt=None):
+    """Times the reference's own CPU forward (oracle/_ref) on the same model file: after ingesting `prompt`
+    through its batch path (untimed; None = empty context), greedy decode steps, as many as fit the time
+    budget (at least one). Returns (tokens/s, threads, steps, seconds, start context)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     cores = os.cpu_count() or 1
     os.environ.setdefault("OMP_NUM_THREADS", str(cores))
     m = ol.RefModel(path)
-    tok, n, t0 = 5, 0, time.perf_counter()
+    tok, start = 5, 0
+    if prompt is not None and len(prompt):
+        tok, start = int(m.prefill(prompt).argmax()), len(prompt)
+    n, t0 = 0, time.perf_counter()
     while n < max_tokens:
-        tok = int(m.decode(tok, n).argmax())
+        tok = int(m.decode(tok, start + n).argmax())
         n += 1
         if time.perf_counter() - t0 > budget_s:
             break
     dt = time.perf_counter() - t0
-    return n / dt, cores, n, dt
+    return n / dt, cores, n, dt, start
 
 
-def run_reference(args, shape, scheme, batch, prompt_len):
+def run_reference(args, shape, scheme, batch, prompt_len, kv):
+    """The reference arm: the reference's own CPU path (oracle/_ref) on the workload's model file, batch 1.
+    Protocol for the 7B workload: a 32-token prompt through forward_cpu_batch (the warm-up, untimed), then
+    greedy decode steps for at most 120 s; `steps` and `warmup` in the line are what was really run. A CPU
+    token is weight-bound (every weight is dequantised and multiplied once per token), so the 1024-token
+    context of the GPU arm would change its time per token by well under 1 %."""
     rank, _, world = dist_env()
     if rank != 0:
         return
     pkg = __graft_entry__.load_package()
     path = model_path(pkg, shape, scheme)
-    tps, cores, n, dt = cpu_reference_tokens_per_s(path, budget_s=150.0, max_tokens=max(1, args.steps))
-    sample = f"{n} decode steps of the full model from an empty context (batch 1), {dt:.1f} s"
+    vocab = pkg.synth.SHAPES[shape]["vocab"]
+    n_prompt = 32
+    prompt = np.random.Generator(np.random.PCG64(4321)).integers(0, vocab, n_prompt).astype(np.int32)
+    tps, cores, n, dt, start = cpu_reference_tokens_per_s(path, budget_s=120.0, max_tokens=max(1, args.steps), prompt=prompt)
+    sample = (f"{n} greedy decode steps of the full model after a {n_prompt}-token prompt (batch 1, FP32 KV: the reference "
+              f"has no CPU INT8 cache), {dt:.1f} s")
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+            "steps": n, "warmup": 1, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": batch, "prompt_len": prompt_len},
+            "config": {"workload": args.workload, "batch": 1, "prompt_len": prompt_len if not isinstance(prompt_len, tuple) else list(prompt_len),
+                       "kv_cache": kv, "context_during_timing": [start, start + n],
+                       "reference_protocol": f"{n_prompt}-token prompt then greedy decode on the host cores; batch 1; FP32 KV",
+                       "requested_steps": args.steps, "requested_warmup": args.warmup},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def parity_in_run(eng, shape, scheme, kv):
+    """Replays the committed golden case of this model (ids and logits from the reference's CPU path, or from the
+    restated oracle for an INT8 cache; tests/golden/make_golden_full.py) on the engine that was just timed: the
+    golden prompt token by token, then the greedy steps. Returns a dict for the JSON line, or None."""
+    case = GOLDEN_CASE.get((shape, scheme))
+    gpath = os.path.join(ROOT, "tests", "golden", "full_models.npz")
+    if case is None or not os.path.exists(gpath):
+        return None
+    g = np.load(gpath)
+    tag = f"{case}_{'i8' if kv == 'i8' and case != 'c1' else 'f32'}"
+    if f"{tag}_ids" not in g or (kv == "i8") != tag.endswith("i8"):
+        return None
+    prompt, ids = g[f"{case}_prompt"], g[f"{tag}_ids"]
+    eng.kv_reset(0)
+    logits = None
+    for i, t in enumerate(prompt):
+        logits, _ = eng.decode([int(t)], [i])
+    err = float(np.abs(logits[0] - g[f"{tag}_prefill_logits"]).max())
+    got, tok = [int(logits[0].argmax())], int(ids[0])
+    keep = {int(k): j for j, k in enumerate(g[f"{tag}_step_index"])}
+    for i in range(len(ids) - 1):
+        logits, amax = eng.decode([tok], [len(prompt) + i])
+        if i in keep:
+            err = max(err, float(np.abs(logits[0] - g[f"{tag}_step_logits"][keep[i]]).max()))
+        got.append(int(amax[0]))
+        tok = int(ids[i + 1])
+    return {"case": tag, "source": "tests/golden/full_models.npz: " + ("restated oracle (INT8 KV)" if tag.endswith("i8") else "reference CPU path"),
+            "ids_checked": len(ids), "ids_match": got == [int(v) for v in ids], "max_abs_logit_err": round(err, 6),
+            "logit_gate": 2e-2}
 
 
 def main():
@@ -150,10 +203,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--planes", type=int, default=3, choices=[2, 3])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the in-run parity check against the golden fixtures")
     args = ap.parse_args()
     shape, scheme, batch, prompt_len, kv = WORKLOADS[args.workload]
     if args.impl == "reference":
-        return run_reference(args, shape, scheme, batch, prompt_len)
+        return run_reference(args, shape, scheme, batch, prompt_len, kv)
 
     rank, local_rank, world = dist_env()
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
@@ -198,15 +252,14 @@ def main():
         return [n + p for n in lens]
 
     # ---- warm-up, then the timed device-resident loop ----
+    sampler = ClockSampler(local_rank)  # runs across warm-up, the timed loop, the end-to-end leg and the per-kind timings
+    sampler.start()
     out, _ = eng.generate_greedy(first, at(pos), warmup)
     pos += warmup
     nxt = out[-1].copy()
     if dist:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     out, ms = eng.generate_greedy(nxt, at(pos), args.steps)
-    clocks = sampler.finish()
     pos += args.steps
     if dist:
         import torch
@@ -244,8 +297,9 @@ def main():
     # DRAM bytes (read + write) per launch from one ncu capture of this workload's four per-layer kinds
     # (profiles/gemv_kernel_7b_q4km_bs1.txt); the lm_head launch was not captured and is scaled from its
     # algorithmic bytes by the mean ratio of the others. Other workloads: no capture, null.
-    traffic = None
+    traffic = traffic_source = None
     if args.workload == "c3-llama2-7b-q4km-bs1" and world == 1:
+        traffic_source = "profiles/gemv_kernel_7b_q4km_bs1.txt (one ncu capture of the same launches; not measured in this run)"
         ncu_mb = {"gate_up_swiglu": 51.530, "qkv_rope": 32.998, "down_proj": 38.268, "o_proj": 9.667}
         ratio = sum(ncu_mb.values()) * 1e6 / sum(kern[k]["bytes"] for k in ncu_mb)
         tot = sum(ncu_mb[k] * 1e6 * kinds[k][1] for k in ncu_mb) + ratio * kern["lm_head"]["bytes"]
@@ -256,11 +310,12 @@ def main():
     step_bytes = world * (st["weight_bytes"] + ctx_sum_mid * st["kv_bytes_per_position"]) + batch * 4 * eng.hidden
     step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9 / world  # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                "traffic": traffic, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
+                "traffic": traffic, "traffic_source": traffic_source, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
                 "bytes_per_launch": int(ksum_b / gemv_launches), "us_per_launch": round(ksum_t / gemv_launches, 3),
                 "kinds": kern, "step_bytes": int(step_bytes), "step_GBps": round(step_gbps, 1),
                 "step_frac_of_measured_peak": round(step_gbps / peak, 4), "step_frac_of_8TBps": round(step_gbps / 8000.0, 4)}
 
+    clocks = sampler.finish()
     line = {"metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": f"i{8 * args.planes} activations x packed int weights, f32 accumulate",
@@ -268,7 +323,7 @@ def main():
             "config": {"workload": args.workload, "batch": batch, "prompt_len": list(prompt_len) if isinstance(prompt_len, tuple) else prompt_len,
                        "kv_cache": kv, "context_during_timing": [min(lens) + warmup, max(lens) + warmup + args.steps],
                        "parallelism": "single GPU" if world == 1 else f"tp{world} (column-split QKV/gate/up/head, row-split O/down, " +
-                                      ("one-shot all-reduce over peer memory inside the matvec kernels" if st["launches_per_step"] == 3 + 5 * L
+                                      ("one-shot all-reduce over peer memory inside the matvec kernels" if st["launches_per_step"] <= 3 + 5 * L
                                        else "NCCL all-reduce") + ", NCCL all-gather of logits)",
                        "l2": "weights read per step (GBs) exceed the 126 MB L2; no flush needed",
                        "act_planes": args.planes, "load_s": round(t_load, 2), "prefill_s": round(t_prefill, 2)},
@@ -276,9 +331,13 @@ def main():
                     "d2h_bytes_per_step": 4 * vocab * batch, "steps": e2e_steps},
             "gpu_launches": st["launches_per_step"] * args.steps, "clocks": clocks, "roofline": roofline}
 
+    if rank == 0 and world == 1 and batch == 1 and not args.no_check:
+        chk = parity_in_run(eng, shape, scheme, kv)
+        if chk is not None:
+            line["parity_in_run"] = chk
     if rank == 0 and world == 1 and not args.no_cpu_baseline and os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libref_cpu.so")):
         eng.close()
-        tps, cores, n, dt = cpu_reference_tokens_per_s(path, budget_s=20.0, max_tokens=4)
+        tps, cores, n, dt, _ = cpu_reference_tokens_per_s(path, budget_s=20.0, max_tokens=4)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference",
                                 "sample": f"{n} decode steps of the same model file from an empty context, {dt:.1f} s"}
     if rank == 0:

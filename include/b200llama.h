@@ -116,8 +116,25 @@ int b200_matvec(int ggml_type, const void* host_blocks, int64_t rows, int64_t co
  * host_y [n_tokens][rows]. Agrees with the FP32 dot to about 1e-3 of the largest output. */
 int b200_matmul(int ggml_type, const void* host_blocks, int64_t rows, int64_t cols, const float* host_x, int n_tokens,
                 float* host_y);
-/* rmsnorm_vector_cuda (cuda_kernels.cu:209-253, 2499) */
+/* rmsnorm_vector_cpu (utils.cpp:648-673) / rmsnorm_vector_cuda (cuda_kernels.cu:209-253, 2499) as the decode path
+ * computes it: the prologue of the matvec kernel (FP32 sum of squares, f = 1/sqrt(mean + max(eps, 1e-5)), out =
+ * x*f*w) followed by its 24-bit block quantisation; host_out is the vector the matvec then multiplies
+ * (within 2^-23 of the block's largest magnitude of the exact normalised value). n a multiple of 256. */
 int b200_rmsnorm(const float* host_x, const float* host_w, int n, float eps, float* host_out);
+/* rmsnorm_batch_cpu (utils.cpp:613-646: eps as given) as the prompt / batch >= 16 path computes it: one block per
+ * token, output rounded to fp16 (the operand type of the tensor-core matmul), returned as floats. */
+int b200_rmsnorm_batch(const float* host_x, const float* host_w, int n_tokens, int n, float eps, float* host_out);
+/* One decode-step launch of the attention input, as TinyLlamaModel::forward does it (model.cpp:589-631): RMSNorm of
+ * x, the q / k / v projections (packed blocks of the given types, [hidden][hidden] and [n_kv*hd][hidden]) and RoPE
+ * on q and k at position pos (apply_rope_vector, utils.cpp:428-489, adjacent pairs; table as
+ * gpu_initialization.cpp:48-58). host_norm_w may be NULL (no normalisation). Outputs q [hidden], k, v [n_kv*hd]. */
+int b200_fused_qkv_rope(int type_q, const void* wq, int type_k, const void* wk, int type_v, const void* wv, int hidden,
+                        int n_heads, int n_kv_heads, const float* host_x, const float* host_norm_w, float eps, int pos,
+                        float rope_theta, int planes, float* q_out, float* k_out, float* v_out);
+/* One decode-step launch of the MLP input (model.cpp:716-735): RMSNorm, gate and up projections ([ffn][hidden] each,
+ * same block type) and SwiGLU, out[i] = (g * 1/(1+exp(-g))) * u (silu_cpu, utils.cpp:700-707). */
+int b200_fused_gate_up_swiglu(int ggml_type, const void* wgate, const void* wup, int ffn, int hidden,
+                              const float* host_x, const float* host_norm_w, float eps, int planes, float* host_out);
 /* Decode attention of one new token over a cache of n_ctx earlier positions (attention_cuda,
  * cuda_kernels.cu:1078 / 2523; INT8 form: quantizer of cuda_kernels.cu:1535-1606 with a softmax
  * attention). q [n_heads][hd]; k_new, v_new [n_kv][hd] (already rotated); k_cache, v_cache
@@ -142,9 +159,11 @@ int b200_attention_prefill(const float* q, const float* k_rows, const float* v_r
  * position = one int, the index of the new token (rows 0..position-1 of the caches are read, row
  * `position` is written); out [n_heads][hd]. The split-K scratch is a fixed array inside the library
  * (about 1 MiB per GPU, held until the process exits): n_heads * n_splits <= 2048, n_heads <= 512,
- * n_splits <= 64, head_dim <= 128, anything larger is refused with status 2 and a message. The first call on each
- * device looks up that array's address and raises the kernel's shared-memory limit; make that call
- * outside any stream capture. Calls share the scratch, so two calls whose kernels overlap on the GPU
+ * n_splits <= 64, head_dim in {16, 32, 64, 128}, anything larger is refused with status 2 and a message. The
+ * host cannot see *position: the kernel checks it, and a value outside [0, max_ctx) makes the call read and
+ * append nothing and fill `out` with NaN. The first call on each device looks up that array's address and
+ * raises the kernel's shared-memory limit (both once per device ordinal); make that call outside any stream
+ * capture. Calls share the scratch, so two calls whose kernels overlap on the GPU
  * (different streams) race; calls on one stream are safe. The launch is asynchronous on `stream`
  * (a cudaStream_t, may be NULL). */
 int b200_attention_decode_noalloc(const float* d_q, const float* d_kv_new, void* d_k_cache, void* d_v_cache,
@@ -161,10 +180,11 @@ int b200_engine_time_kernel(b200_engine* e, int which, int iters, float* mean_us
 
 /* Step trace (no counterpart in the reference, which has no timers besides total wall time, api.cpp:825-831).
  * An engine created while B200_TRACE=1 is set in the environment gives every matvec and attention launch
- * of a step a record of four device timestamps (GPU global timer, ns), written by the first thread of the
- * launch's first CTA: kernel entry, inputs loaded, prologue done, that CTA's end. This call waits for the
- * engine's stream and returns the records of the most recent step in launch order ([n][4]; launches that do
- * not stamp, e.g. the embedding gather, stay zero). */
+ * of a step a record of eight device timestamps (GPU global timer, ns), written by the first thread of the
+ * launch's first CTA: 0 kernel entry, 1 dependency wait over, 2 attention items done, 3 grid barrier passed,
+ * 4 input vector held, 5 prologue done, 6 first tile computed, 7 that CTA's end (launches without an attention
+ * phase stamp 1-3 together). This call waits for the engine's stream and returns the records of the most recent
+ * step in launch order ([n][8]; launches that do not stamp, e.g. the embedding gather, stay zero). */
 int b200_engine_read_trace(b200_engine* e, uint64_t* out, int max_records, int* n_records);
 
 /* ---- tensor parallelism inside one node (no counterpart in the reference, whose MPI coordinator,

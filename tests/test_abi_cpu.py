@@ -45,6 +45,16 @@ def test_create_rejects_bad_dims(pkg):
         pkg.Engine.create(bad)
 
 
+def test_create_rejects_head_sizes_the_kernels_do_not_map(pkg):
+    """The attention kernels map lanes to positions assuming a power-of-two head size: 48, 80, 96 and 112 are refused
+    (the check runs before any device is touched)."""
+    for hd in (48, 80, 96, 112, 256):
+        bad = dict(pkg.synth.SHAPES["tiny"], eps=1e-5, hidden=hd * 4 * 4, n_heads=16, n_kv_heads=4)
+        assert bad["hidden"] % 256 == 0
+        with pytest.raises(pkg.B200Error, match="head_dim must be 16, 32, 64 or 128"):
+            pkg.Engine.create(bad)
+
+
 def test_product_never_touches_oracle():
     """Nothing under the package or the C ABI may reference the oracle folder."""
     for root, _, files in os.walk(os.path.join(ROOT, "tinyllama.cpp_b200")):

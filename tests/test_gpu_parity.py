@@ -89,7 +89,7 @@ def test_matvec_many_tiles_per_cta(pkg, name, rows, cols):
                                                    ("q6_k", 512, 1024, 400)])
 def test_matmul_tensor_core(pkg, name, rows, cols, tokens):
     """The tcgen05 / TMEM matmul (batch >= 16 and prompt path) against the FP64 product of the dequantised
-    weights. Operands are rounded to fp16, so the tolerance is 2e-3 of the largest output (measured 3e-4)."""
+    weights. Operands are rounded to fp16, so the tolerance is 1e-3 of the largest output (measured 3e-4)."""
     typ = TYPES[name]
     w = pkg.synth.fill_normal(rows * cols, 11, rows + typ, 0.02)
     blocks = pkg.synth.quantize(typ, w)
@@ -97,7 +97,7 @@ def test_matmul_tensor_core(pkg, name, rows, cols, tokens):
     wd = ol.dequant("oracle", typ, blocks).reshape(rows, cols)
     ref = (wd.astype(np.float64) @ x.astype(np.float64).T).T
     y = pkg.api.matmul(typ, blocks, rows, cols, x)
-    assert np.abs(y - ref).max() <= 2e-3 * np.abs(ref).max()
+    assert np.abs(y - ref).max() <= 1e-3 * np.abs(ref).max()
 
 
 def test_matvec_batch_and_edge_values(pkg):
@@ -116,14 +116,81 @@ def test_matvec_batch_and_edge_values(pkg):
     assert not y[1].any()
 
 
-def test_rmsnorm(pkg):
-    rng = np.random.default_rng(0)
-    x = rng.standard_normal(4096).astype(np.float32) * 2
-    w = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float32)
+@pytest.mark.parametrize("n", [256, 2048, 4096, 11008, 14336])
+def test_rmsnorm_decode_prologue(pkg, n):
+    """The RMSNorm the decode path runs (prologue of the matvec kernel: FP32 sum of squares, rsqrtf, then the
+    24-bit block quantisation of the activations) against rmsnorm_vector_cpu. Bound: 1e-6 of the largest output
+    (2 ulp of the reciprocal square root + 2^-23 of a block's largest magnitude)."""
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal(n).astype(np.float32) * 2
+    x[5] = 40.0  # an outlier that dominates its block's scale
+    w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
     ref = np.empty_like(x)
     ol.oracle().orc_rmsnorm_vector(ol._p(x), ol._p(w), ol._p(ref), x.size, 1e-5)
     out = pkg.api.rmsnorm(x, w, 1e-5)
     assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
+
+
+def test_rmsnorm_batch_path(pkg):
+    """The RMSNorm of the prompt / batch >= 16 path (one block per token, output rounded to fp16 for the tensor-core
+    matmul) against rmsnorm_batch_cpu: the only difference allowed is the fp16 rounding (2^-11 relative)."""
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((37, 4096)) * 3).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float32)
+    ref = np.empty_like(x)
+    ol.oracle().orc_rmsnorm_batch(ol._p(x), ol._p(w), ol._p(ref), 37, 4096, 1e-5)
+    out = pkg.api.rmsnorm_batch(x, w, 1e-5)
+    assert np.all(np.abs(out - ref) <= 2.0 ** -11 * np.abs(ref) * 1.001 + 1e-7)
+
+
+def _quantized(pkg, typ, rows, cols, seed):
+    w = pkg.synth.fill_normal(rows * cols, seed, rows + typ, 0.02)
+    blocks = pkg.synth.quantize(typ, w)
+    return blocks, ol.dequant("oracle", typ, blocks).reshape(rows, cols)
+
+
+@pytest.mark.parametrize("pos", [0, 1, 777])
+def test_fused_qkv_rope_launch_7b_head_shape(pkg, pos):
+    """RMSNorm + q/k/v projections + RoPE as ONE launch of the decode step, at hidden 4096 / head_dim 128 (q, k Q4_K;
+    v Q6_K; 8 KV heads to keep the CPU side short), against the oracle's composition: rmsnorm_vector, Kahan
+    matvec, apply_rope_vector. Matvec tolerance (1e-3 relative, floor 1e-3 of the largest output)."""
+    H, nq, nkv, hd = 4096, 32, 8, 128
+    bq, wq = _quantized(pkg, 12, H, H, 41)
+    bk, wk = _quantized(pkg, 12, nkv * hd, H, 42)
+    bv, wv = _quantized(pkg, 14, nkv * hd, H, 43)
+    rng = np.random.default_rng(pos)
+    x = rng.standard_normal(H).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    xn = np.empty_like(x)
+    ol.oracle().orc_rmsnorm_vector(ol._p(x), ol._p(nw), ol._p(xn), H, 1e-5)
+    q, k, v = (ol.matvec_f32("oracle", w, xn) for w in (wq, wk, wv))
+    table = ol.rope_table(10000.0, hd, pos + 1)
+    ol.oracle().orc_rope_vector(ol._p(q), nq, hd, pos, ol._p(table), pos + 1)
+    ol.oracle().orc_rope_vector(ol._p(k), nkv, hd, pos, ol._p(table), pos + 1)
+    gq, gk, gv = pkg.api.fused_qkv_rope((12, 12, 14), (bq, bk, bv), H, nq, nkv, x, nw, 1e-5, pos, 10000.0)
+    assert rel_err(gq, q) <= 1e-3
+    assert rel_err(gk, k) <= 1e-3
+    assert rel_err(gv, v) <= 1e-3
+
+
+@pytest.mark.parametrize("typ", [12, 8])
+def test_fused_gate_up_swiglu_launch_7b_shape(pkg, typ):
+    """RMSNorm + gate/up projections + SwiGLU as ONE launch (hidden 4096, FFN 11008) against the oracle's decode
+    expressions (model.cpp:734-735 with silu_cpu): silu(g) * u with the Kahan dot for g and u."""
+    H, F = 4096, 11008
+    bg, wg = _quantized(pkg, typ, F, H, 51)
+    bu, wu = _quantized(pkg, typ, F, H, 52)
+    rng = np.random.default_rng(typ)
+    x = rng.standard_normal(H).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    xn = np.empty_like(x)
+    ol.oracle().orc_rmsnorm_vector(ol._p(x), ol._p(nw), ol._p(xn), H, 1e-5)
+    g, u = ol.matvec_f32("oracle", wg, xn), ol.matvec_f32("oracle", wu, xn)
+    act = np.empty_like(g)
+    ol.oracle().orc_silu(ol._p(g), ol._p(act), F)
+    ref = act * u
+    out = pkg.api.fused_gate_up_swiglu(typ, bg, bu, F, H, x, nw, 1e-5)
+    assert rel_err(out, ref) <= 2e-3  # a product of two outputs that each carry the matvec tolerance
 
 
 @pytest.mark.parametrize("kv_i8", [False, True])
@@ -345,6 +412,24 @@ def test_forward_from_hidden_state(pkg, tiny_models):
     eng.close()
 
 
+@pytest.mark.parametrize("scheme,typ", [(1, 12), (0, 8), (2, 14)])
+def test_quantised_embedding_table(pkg, tmp_path, scheme, typ):
+    """A checkpoint whose token_embd is Q4_K / Q8_0 / Q6_K (as real quantised checkpoints ship it): the lookup returns
+    the reference dequantiser's values bit for bit and the decode logits match the oracle on the same file."""
+    path = pkg.synth.write_gguf(str(tmp_path / "e.gguf"), "tiny", scheme=scheme, embd_quant=True, norm_random=True)
+    g = pkg.gguf.GGUF(path)
+    t = g.tensors["token_embd.weight"]
+    assert t["type"] == typ
+    table = ol.dequant("oracle", typ, t["data"]).reshape(512, 256)
+    eng = pkg.Engine.from_gguf(path)
+    orc = ol.OracleModel.from_gguf(path)
+    for tok in (0, 77, 511):
+        assert np.array_equal(eng.lookup_embedding(tok).view(np.uint32), table[tok].view(np.uint32))
+    ids_e, ids_o, worst, _ = run_greedy(eng, orc, 9, 8)
+    assert worst <= 2e-2 and ids_e == ids_o
+    eng.close()
+
+
 def test_kv_reset_and_errors(pkg, tiny_models):
     eng = pkg.Engine.from_gguf(tiny_models[0], max_ctx=16)
     a, _ = eng.decode([1], [0])
@@ -389,7 +474,7 @@ def test_upload_tensor_path_and_validation(pkg, tiny_models):
 
 
 def test_step_trace_records(pkg, tiny_models, monkeypatch):
-    """B200_TRACE=1: every matvec / attention launch of a step leaves four ordered device timestamps."""
+    """B200_TRACE=1: every matvec / attention launch of a step leaves eight ordered device timestamps."""
     monkeypatch.setenv("B200_TRACE", "1")
     eng = pkg.Engine.from_gguf(tiny_models[1])
     monkeypatch.delenv("B200_TRACE")
@@ -397,7 +482,7 @@ def test_step_trace_records(pkg, tiny_models, monkeypatch):
     eng.decode([5], [1])
     t = eng.read_trace().astype(np.int64)
     L = eng.desc.num_hidden_layers
-    assert len(t) == 3 + 5 * L
+    assert len(t) == 3 + 5 * L  # embed | per layer: QKV, attention, O projection, gate/up, down | lm_head | select
     body = t[1:1 + 5 * L]
     assert (body > 0).all()
     assert (np.diff(body, axis=1) >= 0).all()          # entry <= inputs <= prologue <= end within a launch
@@ -424,7 +509,7 @@ def test_matvec_long_rows_of_the_8b_and_70b_shapes(pkg, name, rows, cols):
     xs = pkg.synth.fill_normal(32 * cols, 33, cols, 1.0).reshape(32, cols)
     ref2 = (wd.astype(np.float64) @ xs.astype(np.float64).T).T
     y2 = pkg.api.matmul(typ, blocks, rows, cols, xs)
-    assert np.abs(y2 - ref2).max() <= 2e-3 * np.abs(ref2).max()
+    assert np.abs(y2 - ref2).max() <= 1e-3 * np.abs(ref2).max()
 
 
 @pytest.mark.parametrize("kv", ["f32", "i8"])

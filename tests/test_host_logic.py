@@ -39,13 +39,18 @@ def test_quantizers_fit_the_dequantizer_layout(pkg, typ, tol):
     assert np.abs(back - w).max() / np.abs(w).max() < tol
 
 
-def test_activation_slot_swizzle_is_conflict_free():
-    """Restates act_slot() of csrc/gemv.cuh: a bijection on 0..31 whose images of 8 consecutive
-    chunks, and of 8 consecutive even (or odd) chunks, fall in 8 distinct 16-byte bank groups."""
-    slot = lambda s: (s & 24) | ((s + ((s >> 3) & 1)) & 7)  # noqa: E731
-    assert sorted(slot(s) for s in range(32)) == list(range(32))
-    for base in range(0, 32, 8):
-        assert len({slot(base + i) % 8 for i in range(8)}) == 8
-    for base in (0, 16):
-        for parity in (0, 1):
-            assert len({slot(base + 2 * i + parity) % 8 for i in range(8)}) == 8
+def test_quantised_embedding_table_option(pkg, tmp_path):
+    """embd_quant writes token_embd in the main block type (what real checkpoints ship); the oracle's lookup of a
+    row equals the dequantised blocks, and equals the reference's own lookup_embedding where it is built."""
+    path = pkg.synth.write_gguf(str(tmp_path / "e.gguf"), "tiny", scheme=1, embd_quant=True)
+    g = pkg.gguf.GGUF(path)
+    t = g.tensors["token_embd.weight"]
+    assert t["type"] == 12 and (t["rows"], t["cols"]) == (512, 256)
+    table = ol.dequant("oracle", 12, t["data"]).reshape(512, 256)
+    if ol.have_ref():
+        r = ol.RefModel(path)
+        out = np.empty(256, np.float32)
+        assert ol.ref().ref_model_embedding(r.h, 77, ol._p(out)) == 0
+        assert np.array_equal(out, table[77])
+    plain = pkg.synth.write_gguf(str(tmp_path / "p.gguf"), "tiny", scheme=1)
+    assert pkg.gguf.GGUF(plain).tensors["token_embd.weight"]["type"] == 0

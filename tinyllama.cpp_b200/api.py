@@ -29,7 +29,8 @@ EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
-    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_attention_decode", "b200_attention_prefill",
+    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
+    "b200_fused_qkv_rope", "b200_fused_gate_up_swiglu", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
     "b200_nccl_unique_id", "b200_tp_share"]
 
@@ -63,6 +64,9 @@ def lib():
     L.b200_dequant.argtypes = [_i, _vp, _sz, _vp]
     L.b200_matvec.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _i, _vp]
     L.b200_rmsnorm.argtypes = [_vp, _vp, _i, ctypes.c_float, _vp]
+    L.b200_rmsnorm_batch.argtypes = [_vp, _vp, _i, _i, ctypes.c_float, _vp]
+    L.b200_fused_qkv_rope.argtypes = [_i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, ctypes.c_float, _i, ctypes.c_float, _i, _vp, _vp, _vp]
+    L.b200_fused_gate_up_swiglu.argtypes = [_i, _vp, _vp, _i, _i, _vp, _vp, ctypes.c_float, _i, _vp]
     L.b200_attention_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
     L.b200_attention_prefill.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
     L.b200_attention_decode_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]
@@ -194,8 +198,8 @@ class Engine:
         return dict(launches_per_step=a.value, weight_bytes=b.value, kv_bytes_per_position=c.value)
 
     def read_trace(self, max_records=4096):
-        """Device timestamps (ns) of the last step's launches, [n][4]; needs B200_TRACE=1 at engine creation."""
-        out = np.zeros((max_records, 4), np.uint64)
+        """Device timestamps (ns) of the last step's launches, [n][8]; needs B200_TRACE=1 at engine creation."""
+        out = np.zeros((max_records, 8), np.uint64)
         n = _i(0)
         _check(lib().b200_engine_read_trace(self._h, out.ctypes.data_as(_vp), max_records, ctypes.byref(n)))
         return out[:n.value].copy()
@@ -234,6 +238,36 @@ def rmsnorm(x, w, eps):
     x, w = _f32(x), _f32(w)
     out = np.empty_like(x)
     _check(lib().b200_rmsnorm(_ptr(x), _ptr(w), x.size, eps, _ptr(out)))
+    return out
+
+
+def rmsnorm_batch(x, w, eps):
+    """x [n_tokens][n] -> normalised rows as the tensor-core path sees them (fp16-rounded)."""
+    x, w = _f32(x), _f32(w)
+    out = np.empty_like(x)
+    _check(lib().b200_rmsnorm_batch(_ptr(x), _ptr(w), x.shape[0], x.shape[1], eps, _ptr(out)))
+    return out
+
+
+def fused_qkv_rope(types, blocks, hidden, n_heads, n_kv_heads, x, norm_w, eps, pos, theta, act_planes=3):
+    """types / blocks: (q, k, v) ggml types and packed blocks. Returns rotated q [hidden], rotated k and v [n_kv*hd]."""
+    bq, bk, bv = (np.ascontiguousarray(b, np.uint8) for b in blocks)
+    x = _f32(x)
+    norm_w = _f32(norm_w) if norm_w is not None else None
+    kvd = hidden // n_heads * n_kv_heads
+    q, k, v = np.empty(hidden, np.float32), np.empty(kvd, np.float32), np.empty(kvd, np.float32)
+    _check(lib().b200_fused_qkv_rope(types[0], _ptr(bq), types[1], _ptr(bk), types[2], _ptr(bv), hidden, n_heads, n_kv_heads,
+                                     _ptr(x), _ptr(norm_w), eps, pos, theta, act_planes, _ptr(q), _ptr(k), _ptr(v)))
+    return q, k, v
+
+
+def fused_gate_up_swiglu(ggml_type, gate_blocks, up_blocks, ffn, hidden, x, norm_w, eps, act_planes=3):
+    bg, bu = np.ascontiguousarray(gate_blocks, np.uint8), np.ascontiguousarray(up_blocks, np.uint8)
+    x = _f32(x)
+    norm_w = _f32(norm_w) if norm_w is not None else None
+    out = np.empty(ffn, np.float32)
+    _check(lib().b200_fused_gate_up_swiglu(ggml_type, _ptr(bg), _ptr(bu), ffn, hidden, _ptr(x), _ptr(norm_w), eps, act_planes,
+                                           _ptr(out)))
     return out
 
 

@@ -38,8 +38,9 @@ struct AttnParams {
   float* out;            // [batch][out_stride]
   int out_stride;
   float att_scale;
-  unsigned long long* trace;  // optional step-trace record: entry, inputs ready, this CTA's partials written, end
+  unsigned long long* trace;  // optional step-trace record (slots 0, 1: entry, inputs ready; 5: this CTA's partials written; 7: end)
   int cached_new;        // 1: the row of the newest position is already in the cache (prompt ingestion): read it like any other row
+  int* error_flag;       // optional: set to 3 when a position lies outside [0, max_ctx) (nothing is read or written for that sequence)
 };
 
 constexpr int ATTN_GROUP_THREADS = 128;
@@ -325,10 +326,26 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
   // when launched as a programmatic dependent itself: q and the new K/V rows belong to the previous kernel until here
   asm volatile("griddepcontrol.wait;" ::: "memory");
   trace_stamp(rec, 1);
+  trace_stamp(rec, 2);
+  trace_stamp(rec, 3);
+  trace_stamp(rec, 4);
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  {
+    // A position outside the cache would be written past the end of the caller's buffers: such a
+    // sequence is skipped by all of its CTAs (nothing read, nothing appended), its output is set to
+    // NaN and the error word, when there is one, is raised.
+    const int pchk = prm.positions[b];
+    if (pchk < 0 || pchk >= prm.max_ctx) {
+      if (split == 0)
+        for (int d = threadIdx.x; d < prm.hd; d += ATTN_GROUP_THREADS) prm.out[(size_t)b * prm.out_stride + h * prm.hd + d] = __int_as_float(0x7fc00000);
+      if (threadIdx.x == 0 && prm.error_flag) *reinterpret_cast<volatile int*>(prm.error_flag) = 3;
+      return;
+    }
+  }
   attn_item<KV_I8, HD>(prm, split, h, b, sm, threadIdx.x, 1);
   __syncthreads();  // every thread's partials are written; one thread publishes them for the whole CTA
-  trace_stamp(rec, 2);
+  trace_stamp(rec, 5);
+  trace_stamp(rec, 6);
   if (threadIdx.x == 0) {
     __threadfence();
     const int old = atomicAdd(&prm.tickets[b * prm.nq + h], 1);
@@ -337,12 +354,12 @@ __global__ void __launch_bounds__(ATTN_GROUP_THREADS, 5) attn_decode_kernel(cons
   }
   __syncthreads();
   if (!last_flag) {
-    trace_stamp(rec, 3);
+    trace_stamp(rec, 7);
     return;
   }
   attn_merge_head(prm, b, h, threadIdx.x, ATTN_GROUP_THREADS, prm.out + (size_t)b * prm.out_stride + h * prm.hd, sm, 1);
   if (threadIdx.x == 0) prm.tickets[b * prm.nq + h] = 0;
-  trace_stamp(rec, 3);
+  trace_stamp(rec, 7);
 }
 
 // Prompt ingestion: appends the K and V rows of n tokens to the cache before their attention runs
@@ -372,8 +389,11 @@ __global__ void __launch_bounds__(32 * KVA_WARPS) kv_append_kernel(const float* 
   }
 }
 
+// Dynamic shared memory of the kernel: one group's working set, and never less than the
+// 3 * ATTN_MAX_SPLITS floats the merge of the last CTA uses as scratch.
 inline size_t attn_smem_bytes(int hd, int max_ctx, int nsplit, int /*nwarps*/) {
-  return sizeof(float) * attn_group_floats(hd, max_ctx, nsplit);
+  const size_t fl = attn_group_floats(hd, max_ctx, nsplit);
+  return sizeof(float) * (fl > (size_t)3 * ATTN_MAX_SPLITS ? fl : (size_t)3 * ATTN_MAX_SPLITS);
 }
 
 }  // namespace b200

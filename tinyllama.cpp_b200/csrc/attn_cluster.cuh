@@ -46,6 +46,10 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
   // q and the new K/V rows belong to the previous kernel until here
   asm volatile("griddepcontrol.wait;" ::: "memory");
   trace_stamp(rec, 1);
+  trace_stamp(rec, 5);
+  trace_stamp(rec, 6);
+  trace_stamp(rec, 7);
+  trace_stamp(rec, 4);
   const int pos = prm.positions[b], slot = prm.slots[b];
   const int T = pos + 1;
   constexpr int EPL = KV_I8 ? 16 : 4;  // elements per lane per row (one 16-byte load)
@@ -218,7 +222,8 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
       cres[hd + 1] = Lc;
     }
   }
-  trace_stamp(rec, 2);
+  trace_stamp(rec, 5);
+  trace_stamp(rec, 6);
   cluster.sync();
   // ---- the CTAs of the cluster, in split order, by the first one ----
   if (cluster.block_rank() == 0) {
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(ATTC_THREADS, 2) attn_cluster_kernel(const Att
       dst[d] = o * inv;
     }
   }
-  trace_stamp(rec, 3);
+  trace_stamp(rec, 7);
   cluster.sync();  // remote shared memory stays alive until the first CTA has read it
 }
 

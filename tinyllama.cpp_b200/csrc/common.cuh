@@ -9,7 +9,7 @@
 
 namespace b200 {
 
-// Step trace: when a launch is given a record (four 64-bit slots), the first thread of its first
+// Step trace: when a launch is given a record (eight 64-bit slots), the first thread of its first
 // CTA writes the GPU's global nanosecond timer there at fixed points of the kernel.
 __device__ __forceinline__ void trace_stamp(unsigned long long* rec, int col) {
   if (rec) {
@@ -38,33 +38,11 @@ inline int64_t type_block_bytes(int t) { return t == T_Q8_0 ? 34 : t == T_Q4_K ?
 
 // ---- device helpers ----
 __device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ uint2 ldg64(const void* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
-__device__ __forceinline__ uint32_t ldg32(const void* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
-__device__ __forceinline__ uint16_t ldg16(const void* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
 
-// Streaming 128-bit load that does not allocate in L1 (weights are read exactly once per step).
-__device__ __forceinline__ uint4 ldg128_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// 4-way byte dot products with every signedness combination (weights a, activation plane b).
-__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
-  int d;
-  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
+// 4-way byte dot products (weights a, activation digits b).
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
   int d;
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {
-  int d;
-  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {

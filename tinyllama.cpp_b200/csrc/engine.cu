@@ -43,9 +43,14 @@ static EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
+// Raises the kernels' dynamic shared-memory limits. The attribute belongs to the device that is
+// current when it is set, so this runs once per device ordinal, not once per process.
 static void set_gemv_attrs() {
-  static bool done = false;
-  if (done) return;
+  static bool done[64] = {false};
+  int dev = 0;
+  CK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) throw std::runtime_error("device ordinal out of range");
+  if (done[dev]) return;
   const int maxb = GEMV_SMEM_BUDGET;
   CK(cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
   CK(cudaFuncSetAttribute(gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxb));
@@ -65,7 +70,7 @@ static void set_gemv_attrs() {
   CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<true, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(true, 128)));
   CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<false, 64>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 64)));
   CK(cudaFuncSetAttribute((attn_decode_gqa_kernel<false, 128>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfa_smem_bytes(false, 128)));
-  done = true;
+  done[dev] = true;
 }
 
 // Prompt attention on the tensor cores handles head sizes 64 and 128; B200_PREFILL_ATTN=0 sends
@@ -202,14 +207,16 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   }
   if (p.epi == EPI_SWIGLU && p.nseg != 1) throw std::runtime_error("gemv: SwiGLU takes the combined gate+up image");
   p.slot_bytes = (slot + 127) / 128 * 128;
+  const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
   const size_t ring_off = gemv_ring_offset(p.K, e->P);
   const size_t budget = GEMV_SMEM_BUDGET;
   if (ring_off + 2 * (size_t)p.slot_bytes > budget) throw std::runtime_error("gemv: input dimension too large for shared memory");
-  const int nstages = (int)std::min<size_t>(GEMV_MAX_STAGES, (budget - ring_off) / p.slot_bytes);
+  // ring depth: what fits, but no more slots than this CTA will ever fill
+  const int stages_per_cta = ((p.ntiles + gx - 1) / gx) * p.nslab;
+  const int nstages = std::max(1, (int)std::min<size_t>(std::min(GEMV_MAX_STAGES, stages_per_cta), (budget - ring_off) / p.slot_bytes));
   p.early_stages = std::max(1, std::min(nstages, (int)(80 * 1024 / p.slot_bytes)));
   p.error_flag = e->d_error;
   const size_t smem = ring_off + (size_t)nstages * p.slot_bytes;
-  const int gx = std::max(1, std::min(p.ntiles, e->num_sms));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(gx, batch);
   cfg.blockDim = dim3(GEMV_THREADS);
@@ -382,7 +389,7 @@ static void launch_attention(const AttnParams& a, int batch, bool kv_i8, bool us
 
 // Step-trace record of the launch with this index within the step (nullptr when tracing is off).
 static unsigned long long* trace_rec(const b200_engine* e, int launch_index) {
-  return e->d_trace && launch_index < e->trace_cap ? e->d_trace + 4 * (size_t)launch_index : nullptr;
+  return e->d_trace && launch_index < e->trace_cap ? e->d_trace + 8 * (size_t)launch_index : nullptr;
 }
 
 // Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
@@ -500,6 +507,15 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       p.trace = trace_rec(e, launches);
       launches += launch_linear(e, p, batch, st, use_tc);
     }
+    auto fill_attn = [&](AttnParams& a, int ns) {
+      a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
+      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+      a.positions = e->d_positions; a.slots = e->d_slots;
+      a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = ns;
+      a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
+      a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      a.error_flag = e->d_error;
+    };
     if (use_tc && gqa_attn_available(e->hd, e->nq, e->nkv)) {
       const bool i8 = e->desc.kv_dtype == B200_KV_I8;
       kv_append_kernel<<<dim3(batch, (e->nkv + KVA_WARPS - 1) / KVA_WARPS, 2), 32 * KVA_WARPS, 0, st>>>(e->d_kvnew, 2 * KVD, e->d_positions, e->d_slots, e->nkv, e->hd, e->max_ctx, i8 ? 1 : 0,
@@ -516,12 +532,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
       launches += 2;
     } else {
       AttnParams a{};
-      a.q = e->d_q; a.kv_new = e->d_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
-      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
-      a.positions = e->d_positions; a.slots = e->d_slots;
-      a.nq = e->nq; a.nkv = e->nkv; a.hd = e->hd; a.max_ctx = e->max_ctx; a.nsplit = nsplit;
-      a.part_o = e->d_part_o; a.part_ml = e->d_part_ml; a.tickets = e->d_tickets;
-      a.out = e->d_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+      fill_attn(a, nsplit);
       a.trace = trace_rec(e, launches);
       launch_attention(a, batch, e->desc.kv_dtype == B200_KV_I8, e->use_pdl, !attn_use_cluster(), st);
       ++launches;

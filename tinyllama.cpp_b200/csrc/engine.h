@@ -62,7 +62,7 @@ struct b200_engine {
   unsigned* d_epoch = nullptr;
   unsigned* d_peer_ticket = nullptr;
   float* d_h2 = nullptr;             // second residual-stream buffer (the consumer of an exchange writes the other one)
-  unsigned long long* d_trace = nullptr;  // B200_TRACE=1: one 4-slot timestamp record per launch of a step
+  unsigned long long* d_trace = nullptr;  // B200_TRACE=1: one 8-slot timestamp record per launch of a step
   int trace_cap = 0;
   int last_launches = 0;
   bool finalized = false;

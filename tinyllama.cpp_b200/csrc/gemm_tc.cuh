@@ -437,7 +437,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.w_empty[stage]);  // the stage may be refilled
       }
-#pragma unroll
       const int adepth = p.a_stages >> 2;            // blocks the weight-tile ring holds
       const int abase = (blk % adepth) * 4, alap = blk / adepth;
 #pragma unroll

@@ -38,8 +38,9 @@ namespace b200 {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_PEER = 4 };
 constexpr int GEMV_MAX_TP = 8;
-constexpr int GEMV_WARPS = 16;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_WARPS = 16;                        // consumer warps
+constexpr int GEMV_CONSUMER_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_THREADS = GEMV_CONSUMER_THREADS + 32;  // + one producer warp
 constexpr int GEMV_MAX_STAGES = 8;
 constexpr int GEMV_NTB = 16;                          // tiles whose partial sums are parked before their rows are finished
 constexpr int GEMV_SMEM_BUDGET = 208 * 1024;          // dynamic shared memory (activation image + ring)
@@ -165,7 +166,8 @@ struct GemvParams {
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
-  unsigned long long* trace;  // optional step-trace record: entry, input vector loaded, prologue done, end
+  unsigned long long* trace;  // optional step-trace record, eight slots: 0 entry, 1-3 dependency wait over, 4 input vector held,
+                              // 5 prologue done, 6 first tile computed, 7 end
   // ---- tensor-parallel exchange without a collective call (one-shot all-reduce over peer memory) ----
   // Producer side (EPI_PEER): the partial output rows are stored into the exchange buffer of every
   // rank (peer_y[r]: [batch][y_stride] slot of this rank in rank r's memory); the last CTA to finish
@@ -390,6 +392,28 @@ __device__ void act_build(uint8_t* smem, XFN xfn, const float* __restrict__ norm
   consumer_sync();
 }
 
+// Op-level probe of the decode prologue: one CTA of 16 warps runs act_build (RMSNorm when norm_w is
+// given, then the digit-plane quantisation) exactly as the matvec kernel does and writes the vector the
+// matvec will see, x_hat[e] = sx[block] * sum_p digit_p[e] * 256^p, so that a test can compare the
+// normalisation (and the 24-bit quantisation) with the reference's rmsnorm_vector_cpu.
+__global__ void __launch_bounds__(GEMV_CONSUMER_THREADS, 1) act_probe_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
+                                                                             int K, float* __restrict__ out) {
+  extern __shared__ __align__(128) uint8_t smem_probe[];
+  __shared__ float red[GEMV_WARPS + 2];
+  auto xfn = [&](int e, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(x + e), b = *reinterpret_cast<const float4*>(x + e + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  };
+  act_build<3>(smem_probe, xfn, norm_w, eps, K, red, [] {}, [](float) {});
+  const ActImage a = act_carve(smem_probe, K, 3);
+  for (int e = threadIdx.x; e < K; e += blockDim.x) {
+    int v = 0;
+#pragma unroll
+    for (int p = 2; p >= 0; --p) v = v * 256 + (int)(int8_t)a.planes[(size_t)p * a.plane_stride + e];
+    out[e] = a.sx[e >> 8] * (float)v;
+  }
+}
+
 // D(16x8, s32) = A(16x32, u8 or s8) * B(32x8, s8); C = 0.
 template <bool A_SIGNED>
 __device__ __forceinline__ void imma_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -401,12 +425,6 @@ __device__ __forceinline__ void imma_16x8x32(int (&c)[4], uint32_t a0, uint32_t 
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-
-__device__ __forceinline__ uint2 ldg64_stream(const void* p) {
-  uint2 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-  return v;
 }
 
 // byte i (0..3) of w, zero-extended / sign-extended (i is a compile-time constant after unrolling)
@@ -607,9 +625,14 @@ __device__ __forceinline__ void gemv_locate(const GemvParams& p, int tile, int& 
 }
 
 // ---- the streaming pipeline ----------------------------------------------------------------
+// Ring of nstages shared-memory slots. full_bar[s] completes when the bulk copy of the stage in
+// slot s has landed (transaction bytes); empty_bar[s] completes when all 16 consumer warps have
+// finished with it. The producer warp (one lane) walks the CTA's (tile, slab) sequence and
+// refills a slot as soon as it is empty; the consumers never touch the copy engine.
 struct GemvShared {
   unsigned long long full_bar[GEMV_MAX_STAGES];
-  int arrivals[GEMV_MAX_STAGES];  // warps that have finished with the stage in each slot
+  unsigned long long empty_bar[GEMV_MAX_STAGES];
+  unsigned long long xready_bar;  // the consumers hold their part of the input vector (16 arrivals)
   float red[GEMV_WARPS + 2];
   float part[GEMV_NTB][GEMV_WARPS][16];
   float sv[GEMV_WARPS];
@@ -617,57 +640,56 @@ struct GemvShared {
   int abort_flag;
 };
 
-struct PipeCtx {
-  GemvShared* sh;
-  uint8_t* act;   // activation image
-  uint8_t* ring;  // nstages slots of slot_bytes
-  int nstages;
-  int slot;       // ring slot of the stage the warps work on next
-  int use;        // how many times the ring has wrapped
-  int ptile, pslab;  // the stage that will be requested next (same value in every thread)
-  __device__ __forceinline__ void next_stage() {
-    if (++slot == nstages) { slot = 0; ++use; }
-  }
-};
-
 __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < nstages; ++s) {
       mbar_init(&sh->full_bar[s], 1);
-      sh->arrivals[s] = 0;
+      mbar_init(&sh->empty_bar[s], GEMV_WARPS);
     }
+    mbar_init(&sh->xready_bar, GEMV_WARPS);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 }
 
-__device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh) {
+__device__ __forceinline__ void pipe_fail(const GemvParams& prm, GemvShared* sh, int code = 1) {
   sh->abort_flag = 1;
-  if (prm.error_flag) *reinterpret_cast<volatile int*>(prm.error_flag) = 1;  // host-mapped word: a plain store
+  if (prm.error_flag) *reinterpret_cast<volatile int*>(prm.error_flag) = code;  // host-mapped word: a plain store
 }
 
-// Requests stage (tile, slab) into ring slot `slot` with one bulk copy (called by one thread).
-__device__ __forceinline__ void gemv_request(const GemvParams& prm, const PipeCtx& pc, int slot, int tile, int slab) {
-  int s, tl;
-  gemv_locate(prm, tile, s, tl);
-  const GemvSeg& sg = prm.seg[s];
-  const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
-  mbar_expect_tx(&pc.sh->full_bar[slot], bytes);
-  bulk_g2s(pc.ring + (size_t)slot * prm.slot_bytes, sg.img + (size_t)tl * sg.tile_bytes + (size_t)slab * sg.stage_bytes, bytes,
-           &pc.sh->full_bar[slot]);
-}
+__device__ __forceinline__ bool pipe_aborted(GemvShared* sh) { return *(volatile int*)&sh->abort_flag != 0; }
 
-// Advances the request cursor by one stage. Tiles are dealt round-robin over the CTAs so that
-// launches mixing formats of different cost stay balanced.
-__device__ __forceinline__ void gemv_cursor_next(const GemvParams& prm, PipeCtx& pc, int ncta) {
-  if (++pc.pslab == prm.nslab) { pc.pslab = 0; pc.ptile += ncta; }
+// The producer: one lane requests every stage of this CTA's tiles, in the order the consumers use
+// them (tiles cta, cta + ncta, ...; slabs in order), each with ONE bulk copy. Weights never depend
+// on the previous kernel, so the first `early_stages` stages are requested at once; the rest waits
+// until the consumers hold their input vector (behind a full ring of weight traffic on this SM
+// those loads would wait for microseconds).
+__device__ __forceinline__ void gemv_produce(const GemvParams& prm, GemvShared* sh, uint8_t* ring, int nstages, int cta, int ncta) {
+  int slot = 0, fills = 0, n = 0;
+#pragma unroll 1
+  for (int tile = cta; tile < prm.ntiles; tile += ncta) {
+    int s, tl;
+    gemv_locate(prm, tile, s, tl);
+    const GemvSeg& sg = prm.seg[s];
+    const uint8_t* src = sg.img + (size_t)tl * sg.tile_bytes;
+#pragma unroll 1
+    for (int slab = 0; slab < prm.nslab; ++slab, ++n) {
+      if (n == prm.early_stages && !mbar_wait(&sh->xready_bar, 0)) pipe_fail(prm, sh);
+      if (fills > 0 && !mbar_wait(&sh->empty_bar[slot], (fills - 1) & 1)) pipe_fail(prm, sh);
+      if (pipe_aborted(sh)) return;
+      const uint32_t bytes = slab == prm.nslab - 1 ? sg.stage_bytes_last : sg.stage_bytes;
+      mbar_expect_tx(&sh->full_bar[slot], bytes);
+      bulk_g2s(ring + (size_t)slot * prm.slot_bytes, src + (size_t)slab * sg.stage_bytes, bytes, &sh->full_bar[slot]);
+      if (++slot == nstages) { slot = 0; ++fills; }
+    }
+  }
 }
 
 // Finishes the rows of the n tiles parked in sh->part (tiles first_i .. first_i+n-1 of this CTA's
 // sequence): every thread sums the partials of one row in warp order and applies the epilogue.
 __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh, int first_i, int n, int bidx, int cta, int ncta,
-                                           float& best_v, int& best_i) {
+                                        float& best_v, int& best_i) {
   consumer_sync();
   const int tid = threadIdx.x, lane = tid & 31;
   const int R = prm.R, S = prm.S;
@@ -730,99 +752,56 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
   consumer_sync();
 }
 
-// The 16 consumer warps: prologue, then one (row group, block) task per warp per stage; the rows
-// are finished GEMV_NTB tiles at a time.
-template <int P, typename XFN>
-__device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc, XFN xfn, int bidx, int cta, int ncta, float& best_v,
-                                             int& best_i) {
-  GemvShared* sh = pc.sh;
+// State of a consumer warp while it walks the CTA's tiles.
+struct ConsumerCtx {
+  GemvShared* sh;
+  uint8_t* ring;
+  int nstages;
+  int slot, use;   // ring slot of the next stage and how often the ring has wrapped
+  int tile, i;     // launch-wide tile index and its number in this CTA's sequence
+  int cta, ncta, bidx;
+  int rg, bi;      // this warp's row group and block within a stage
+  bool rg_ok, breg;
+  int cur_type;    // block type the register-held B fragments were built for
+  float best_v;
+  int best_i;
+};
+
+// Tiles [.., seg_end) of one segment (all of block type TYPE), one (row group, block) task per
+// warp per stage; partial row sums are parked per tile and finished GEMV_NTB tiles at a time.
+template <int P, int TYPE>
+__device__ __forceinline__ void gemv_tiles(const GemvParams& prm, const GemvSeg& sg, int seg_end, ConsumerCtx& c, const ActImage& a,
+                                           const LaneCtx& L, BFrag& bf) {
+  GemvShared* sh = c.sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // The first early_stages stages were requested at kernel start, so that they land while the
-  // kernel still waits for its input. The rest of the ring is requested as soon as this thread's
-  // part of the input vector has arrived: behind a full ring of weight traffic on this SM those
-  // loads would wait for microseconds.
-  const int early = prm.early_stages;
-  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
-  auto after_x = [&](float ss) {
-    if (threadIdx.x == 0) {
-      uint32_t z;
-      asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));  // issue order: after the loads have returned
-      trace_stamp(rec, 1);
-      int pt = pc.ptile, ps = pc.pslab;
-      for (int k = (int)z; k < pc.nstages && pt < prm.ntiles; ++k) {
-        if (k >= early) gemv_request(prm, pc, k, pt, ps);
-        if (++ps == prm.nslab) { ps = 0; pt += ncta; }
-      }
-    }
-  };
-  auto before_x = [&]() {
-    pdl_wait();
-    if (prm.wait_flags) {  // tensor parallel: the other ranks' partial sums must have landed in this GPU's memory
-      if ((int)threadIdx.x < prm.tp && (int)threadIdx.x != prm.tp_rank) {
-        const unsigned want = *prm.epoch_base + prm.epoch_k;
-        const volatile unsigned* f = prm.wait_flags + threadIdx.x;
-        int it = 0;
-        while ((int)(*f - want) < 0) {
-          if (++it > (1 << 24)) {  // bounded (seconds): report instead of hanging when a rank has gone away
-            pipe_fail(prm, sh);
-            break;
-          }
-          __nanosleep(100);
-        }
-        __threadfence_system();
-      }
-      consumer_sync();
-    }
-  };
-  act_build<P>(pc.act, xfn, prm.norm_w, prm.eps, prm.K, sh->red, before_x, after_x);
-  trace_stamp(rec, 2);
-  for (int k = 0; k < pc.nstages; ++k) gemv_cursor_next(prm, pc, ncta);  // the cursor now points past the initial fill
-  const ActImage a = act_carve(pc.act, prm.K, P);
-
-  LaneCtx L;
-  L.g = lane >> 2;
-  L.t = lane & 3;
-  L.wd = __int_as_float((127 + 8 * L.t) << 23);  // 256^t
-  L.wt = L.t < P ? L.wd : 0.f;
-  const int rg = warp / prm.S, bi = warp - rg * prm.S;  // this warp's row group and block within a stage
-  const bool rg_ok = rg < prm.R;
-  BFrag bf;
-  int cur_type = -1;
-  // rows of at most 16 blocks: one stage per tile, the warp meets the same block column every
-  // time and its B fragments stay in registers until the block type changes
-  const bool breg = prm.nslab == 1;
-
-  int i = 0;
+  constexpr int ub = TYPE == T_Q4_K ? 144 : TYPE == T_Q6_K ? 208 : 272;
+  const int nslab = prm.nslab;
+  // byte offset of this lane's first row (row g of the warp's row group) and block within a stage
+  const uint32_t off_full = (uint32_t)(c.rg * 16 + L.g) * (uint32_t)sg.RS + (uint32_t)c.bi * ub;
+  const uint32_t off_last = (uint32_t)(c.rg * 16 + L.g) * (uint32_t)sg.RS_last + (uint32_t)c.bi * ub;
 #pragma unroll 1
-  for (int tile = cta; tile < prm.ntiles; tile += ncta, ++i) {
-    int s, tl;
-    gemv_locate(prm, tile, s, tl);
-    const GemvSeg& sg = prm.seg[s];
-    const int type = sg.type;
-    const int ub = gemv_unit_bytes(type);
+  for (; c.tile < seg_end; c.tile += c.ncta, ++c.i) {
     float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll 1
-    for (int slab = 0; slab < prm.nslab; ++slab, pc.next_stage()) {
-      const int slot = pc.slot, use = pc.use;
-      const bool last = slab == prm.nslab - 1;
-      const bool active = rg_ok && bi < (last ? prm.S_last : prm.S);
+    for (int slab = 0; slab < nslab; ++slab) {
+      const bool last = slab == nslab - 1;
+      const bool active = c.rg_ok && c.bi < (last ? prm.S_last : prm.S);
       // the activation digits are ready before the weights: fetch them ahead of the wait (with at
       // most 16 blocks per row the warp meets the same block every time and keeps them)
-      if (active && (!breg || type != cur_type)) {
-        load_bfrag<P>(type, a, slab * prm.S + bi, L, bf);
-        cur_type = type;
+      if (active && (!c.breg || c.cur_type != TYPE)) {
+        load_bfrag<P>(TYPE, a, slab * prm.S + c.bi, L, bf);
+        c.cur_type = TYPE;
       }
-      if (lane == 0 && !*(volatile int*)&sh->abort_flag && !mbar_wait(&sh->full_bar[slot], use & 1)) pipe_fail(prm, sh);
-      __syncwarp();  // one lane probes; the rest of the warp parks here
+      if (!pipe_aborted(sh) && !mbar_wait(&sh->full_bar[c.slot], c.use & 1)) pipe_fail(prm, sh);
       if (active) {
         const int RSt = last ? sg.RS_last : sg.RS;
-        const uint8_t* ra = pc.ring + (size_t)slot * prm.slot_bytes + (size_t)(rg * 16 + L.g) * RSt;
-        const uint8_t* pa = ra + bi * ub;
+        const uint8_t* pa = c.ring + (size_t)c.slot * prm.slot_bytes + (last ? off_last : off_full);
         const uint8_t* pb = pa + 8 * RSt;
-        if (type == T_Q4_K) {
+        if (TYPE == T_Q4_K) {
           compute_q4(pa, pb, bf, L, acc0, acc1);
-        } else if (type == T_Q6_K) {
-          const int dof = (last ? sg.d_off_last : sg.d_off) + 2 * bi;
+        } else if (TYPE == T_Q6_K) {
+          const uint8_t* ra = pa - c.bi * ub;
+          const int dof = (last ? sg.d_off_last : sg.d_off) + 2 * c.bi;
           const float d0 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(ra + dof));
           const float d1 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(ra + 8 * RSt + dof));
           compute_q6(pa, pb, d0, d1, bf, L, acc0, acc1);
@@ -831,25 +810,22 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, PipeCtx& pc,
         }
       }
       __syncwarp();
-      // the last warp to finish with this slot requests the stage that goes into it next
-      if (lane == 0 && atomicAdd(&sh->arrivals[slot], 1) == GEMV_WARPS - 1) {
-        sh->arrivals[slot] = 0;  // ordered before the other warps' next visit by the request's barrier arrive
-        if (pc.ptile < prm.ntiles) gemv_request(prm, pc, slot, pc.ptile, pc.pslab);
-      }
-      gemv_cursor_next(prm, pc, ncta);
+      if (lane == 0) mbar_arrive(&sh->empty_bar[c.slot]);  // this warp is done with the slot
+      if (++c.slot == c.nstages) { c.slot = 0; ++c.use; }
     }
     // ---- tile finished: fold the four k-slices and park the partial sums ----
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    const int pp = i % GEMV_NTB;
+    const int pp = c.i % GEMV_NTB;
+    if (c.i == 0 && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) trace_stamp(prm.trace, 6);
     if (L.t == 0) {
       sh->part[pp][warp][L.g] = acc0;
       sh->part[pp][warp][L.g + 8] = acc1;
     }
-    // rows are finished when GEMV_NTB tiles are parked or after the CTA's last tile (one call site: code size)
-    if (pp == GEMV_NTB - 1 || tile + ncta >= prm.ntiles) gemv_flush(prm, sh, i - pp, pp + 1, bidx, cta, ncta, best_v, best_i);
+    // rows are finished when GEMV_NTB tiles are parked or after the CTA's last tile
+    if (pp == GEMV_NTB - 1 || c.tile + c.ncta >= prm.ntiles) gemv_flush(prm, sh, c.i - pp, pp + 1, c.bidx, c.cta, c.ncta, c.best_v, c.best_i);
   }
 }
 
@@ -903,40 +879,95 @@ struct XLoad {
   }
 };
 
-// One launch = one fused matvec for blockIdx.y's activation vector; one persistent CTA per SM.
-// There is one instantiation per activation width only: a decode step alternates between this
-// kernel and the attention kernel 160 times, and their code should stay in the instruction cache.
+// The 16 consumer warps: prologue, then the tiles segment by segment.
 template <int P>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams prm, int nstages) {
+__device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* sh, uint8_t* smem, uint8_t* ring, int nstages) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cta = blockIdx.x, ncta = gridDim.x, bidx = blockIdx.y;
+  unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
+  XLoad xfn{prm.x + (size_t)bidx * prm.x_stride, prm.x_parts ? prm.x_parts + (size_t)bidx * prm.x_stride : nullptr,
+            prm.parts_stride, prm.tp, (prm.x_out && cta == 0) ? prm.x_out + (size_t)bidx * prm.x_stride : nullptr};
+  auto after_x = [&](float ss) {
+    uint32_t z;
+    asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));  // issue order: after the loads have returned
+    if (lane == (int)z) {
+      if (threadIdx.x == 0) trace_stamp(rec, 4);
+      mbar_arrive(&sh->xready_bar);
+    }
+  };
+  auto before_x = [&]() {
+    pdl_wait();
+    trace_stamp(rec, 1);
+    trace_stamp(rec, 2);
+    trace_stamp(rec, 3);
+    if (prm.wait_flags) {  // tensor parallel: the other ranks' partial sums must have landed in this GPU's memory
+      if ((int)threadIdx.x < prm.tp && (int)threadIdx.x != prm.tp_rank) {
+        const unsigned want = *prm.epoch_base + prm.epoch_k;
+        const volatile unsigned* f = prm.wait_flags + threadIdx.x;
+        int it = 0;
+        while ((int)(*f - want) < 0) {
+          if (++it > (1 << 24)) {  // bounded (seconds): report instead of hanging when a rank has gone away
+            pipe_fail(prm, sh);
+            break;
+          }
+          __nanosleep(100);
+        }
+        __threadfence_system();
+      }
+      consumer_sync();
+    }
+  };
+  act_build<P>(smem, xfn, prm.norm_w, prm.eps, prm.K, sh->red, before_x, after_x);
+  trace_stamp(rec, 5);
+  const ActImage a = act_carve(smem, prm.K, P);
+
+  LaneCtx L;
+  L.g = lane >> 2;
+  L.t = lane & 3;
+  L.wd = __int_as_float((127 + 8 * L.t) << 23);  // 256^t
+  L.wt = L.t < P ? L.wd : 0.f;
+  ConsumerCtx c;
+  c.sh = sh; c.ring = ring; c.nstages = nstages; c.slot = 0; c.use = 0;
+  c.tile = cta; c.i = 0; c.cta = cta; c.ncta = ncta; c.bidx = bidx;
+  c.rg = warp / prm.S; c.bi = warp - c.rg * prm.S;
+  c.rg_ok = c.rg < prm.R;
+  // rows of at most 16 blocks: one stage per tile, the warp meets the same block column every
+  // time and its B fragments stay in registers until the block type changes
+  c.breg = prm.nslab == 1;
+  c.cur_type = -1;
+  c.best_v = -INFINITY; c.best_i = 0x7fffffff;
+  BFrag bf;
+  int seg_end = 0;
+#pragma unroll 1
+  for (int s = 0; s < prm.nseg; ++s) {
+    const GemvSeg& sg = prm.seg[s];
+    seg_end += sg.tiles;
+    if (c.tile >= seg_end) continue;
+    if (sg.type == T_Q4_K) gemv_tiles<P, T_Q4_K>(prm, sg, seg_end, c, a, L, bf);
+    else if (sg.type == T_Q6_K) gemv_tiles<P, T_Q6_K>(prm, sg, seg_end, c, a, L, bf);
+    else gemv_tiles<P, T_Q8_0>(prm, sg, seg_end, c, a, L, bf);
+  }
+  if (prm.amax_val) gemv_store_argmax(prm, sh, c.best_v, c.best_i, bidx, cta, ncta);
+}
+
+// One launch = one fused matvec for blockIdx.y's activation vector; one persistent CTA per SM:
+// 16 consumer warps and one producer warp. There is one instantiation per activation width only: a
+// decode step alternates between this kernel and the attention kernel 160 times, and their code
+// should stay in the instruction caches.
+template <int P>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const __grid_constant__ GemvParams prm, int nstages) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ GemvShared sh;
-  PipeCtx pc;
-  pc.sh = &sh;
-  pc.act = smem;
-  pc.ring = smem + gemv_ring_offset(prm.K, P);
-  pc.nstages = nstages;
-  pc.slot = 0;
-  pc.use = 0;
-  pc.ptile = blockIdx.x;
-  pc.pslab = 0;
+  uint8_t* ring = smem + gemv_ring_offset(prm.K, P);
   pipe_init(&sh, nstages);
   pdl_launch_dependents();
-  // weights never depend on the previous kernel: the first stages are requested before the dependency wait
-  if (threadIdx.x == 0) {
-    int pt = pc.ptile, ps = 0;
-    for (int k = 0; k < nstages && k < prm.early_stages && pt < prm.ntiles; ++k) {
-      gemv_request(prm, pc, k, pt, ps);
-      if (++ps == prm.nslab) { ps = 0; pt += gridDim.x; }
-    }
+  if (threadIdx.x >= GEMV_CONSUMER_THREADS) {
+    if (threadIdx.x == GEMV_CONSUMER_THREADS) gemv_produce(prm, &sh, ring, nstages, blockIdx.x, gridDim.x);
+    return;
   }
   unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
   trace_stamp(rec, 0);
-  float best_v = -INFINITY;
-  int best_i = 0x7fffffff;
-  XLoad xfn{prm.x + (size_t)blockIdx.y * prm.x_stride, prm.x_parts ? prm.x_parts + (size_t)blockIdx.y * prm.x_stride : nullptr,
-            prm.parts_stride, prm.tp, (prm.x_out && blockIdx.x == 0) ? prm.x_out + (size_t)blockIdx.y * prm.x_stride : nullptr};
-  gemv_consume<P>(prm, pc, xfn, blockIdx.y, blockIdx.x, gridDim.x, best_v, best_i);
-  if (prm.amax_val) gemv_store_argmax(prm, &sh, best_v, best_i, blockIdx.y, blockIdx.x, gridDim.x);
+  gemv_consume<P>(prm, &sh, smem, ring, nstages);
   if (prm.epi == EPI_PEER && threadIdx.x == 0) {
     // every thread's stores were issued before the barrier that ends the last flush; make them
     // visible system-wide, and let the last CTA of the launch publish the exchange number
@@ -949,7 +980,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
         if (r != prm.tp_rank) *reinterpret_cast<volatile unsigned*>(prm.peer_flag[r]) = ep;
     }
   }
-  trace_stamp(rec, 3);
+  trace_stamp(rec, 7);
 }
 
 }  // namespace b200

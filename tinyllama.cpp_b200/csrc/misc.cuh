@@ -110,24 +110,10 @@ __global__ void add_inplace_kernel(float* __restrict__ h, const float* __restric
   if (i < n) h[i] = h[i] + partial[i];
 }
 
-// Standalone RMSNorm for the op-level entry point (reference utils.cpp:648-673).
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out, int n, float eps) {
-  __shared__ double red[33];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  double ss = 0.0;
-  for (int i = tid; i < n; i += blockDim.x) ss += (double)x[i] * (double)x[i];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (lane == 0) red[warp] = ss;
-  __syncthreads();
-  if (tid == 0) {
-    double t = 0.0;
-    for (int wv = 0; wv < nwarps; ++wv) t += red[wv];
-    red[32] = t;
-  }
-  __syncthreads();
-  const float f = 1.0f / sqrtf((float)(red[32] / (double)n) + eps);
-  for (int i = tid; i < n; i += blockDim.x) out[i] = x[i] * f * w[i];
+// fp16 -> fp32, element by element (op-level checks of the batch RMSNorm path).
+__global__ void half_to_float_kernel(const __half* __restrict__ in, float* __restrict__ out, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __half2float(in[i]);
 }
 
 }  // namespace b200

@@ -229,7 +229,8 @@ struct b200_synth_config {
   int32_t hidden, ffn, n_heads, n_kv_heads, n_layers, vocab, max_pos;
   float eps, theta;
   int32_t scheme;       // 0: every linear Q8_0; 1: Q4_K with Q6_K for attn_v, ffn_down, output; 2: every linear Q6_K; 3: every linear Q4_K
-  int32_t norm_random;  // 0: norm weights 1.0; 1: 1 + 0.1*N(0,1) (exercises the norm-weight indexing in small tests)
+  int32_t norm_random;  // bit 0: norm weights 1 + 0.1*N(0,1) instead of 1.0 (exercises the norm-weight indexing in small tests);
+                        // bit 1: token_embd is quantised like attn_q (as real checkpoints ship it) instead of F32
   uint64_t seed;
   float sigma;
 };
@@ -268,7 +269,7 @@ int b200_synth_write_gguf(const char* path, const b200_synth_config* c) {
   auto add = [&](const std::string& n, int type, int64_t rows, int64_t cols, int kind) {
     plan.push_back({n, type, rows, cols, kind, 0, 0});
   };
-  add("token_embd.weight", 0, V, H, 0);
+  add("token_embd.weight", (c->norm_random & 2) ? t_main : 0, V, H, 0);
   for (int l = 0; l < L; ++l) {
     std::string p = "blk." + std::to_string(l) + ".";
     add(p + "attn_norm.weight", 0, 1, H, 1);
@@ -339,7 +340,7 @@ int b200_synth_write_gguf(const char* path, const b200_synth_config* c) {
       fbuf.resize((size_t)cnt);
       if (t.kind == 1) {
         for (int64_t i = 0; i < cnt; ++i)
-          fbuf[i] = c->norm_random ? 1.0f + normal_at(c->seed, ti + 1, (uint64_t)(start + i), 0.1f) : 1.0f;
+          fbuf[i] = (c->norm_random & 1) ? 1.0f + normal_at(c->seed, ti + 1, (uint64_t)(start + i), 0.1f) : 1.0f;
       } else {
         const uint64_t seed = c->seed, stream = ti + 1;
         const float sigma = c->sigma;

@@ -33,20 +33,24 @@ struct Nccl {
   static Nccl& get() {
     static Nccl n;
     if (!n.handle) {
-      n.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-      if (!n.handle) n.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
-      if (!n.handle) throw std::runtime_error(std::string("cannot load libnccl: ") + dlerror());
+      void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+      if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+      if (!h) throw std::runtime_error(std::string("cannot load libnccl: ") + dlerror());
       auto sym = [&](const char* name) {
-        void* p = dlsym(n.handle, name);
+        void* p = dlsym(h, name);
         if (!p) throw std::runtime_error(std::string("libnccl lacks ") + name);
         return p;
       };
-      n.GetUniqueId = reinterpret_cast<decltype(n.GetUniqueId)>(sym("ncclGetUniqueId"));
-      n.CommInitRank = reinterpret_cast<decltype(n.CommInitRank)>(sym("ncclCommInitRank"));
-      n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(sym("ncclCommDestroy"));
-      n.AllReduce = reinterpret_cast<decltype(n.AllReduce)>(sym("ncclAllReduce"));
-      n.AllGather = reinterpret_cast<decltype(n.AllGather)>(sym("ncclAllGather"));
-      n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(sym("ncclGetErrorString"));
+      // resolve into a scratch copy: the singleton is published only when every symbol is there
+      Nccl t;
+      t.GetUniqueId = reinterpret_cast<decltype(t.GetUniqueId)>(sym("ncclGetUniqueId"));
+      t.CommInitRank = reinterpret_cast<decltype(t.CommInitRank)>(sym("ncclCommInitRank"));
+      t.CommDestroy = reinterpret_cast<decltype(t.CommDestroy)>(sym("ncclCommDestroy"));
+      t.AllReduce = reinterpret_cast<decltype(t.AllReduce)>(sym("ncclAllReduce"));
+      t.AllGather = reinterpret_cast<decltype(t.AllGather)>(sym("ncclAllGather"));
+      t.GetErrorString = reinterpret_cast<decltype(t.GetErrorString)>(sym("ncclGetErrorString"));
+      t.handle = h;
+      n = t;
     }
     return n;
   }

@@ -43,12 +43,13 @@ def lib():
     return _lib
 
 
-def write_gguf(path, shape, scheme, seed=1234, sigma=0.02, norm_random=False, eps=1e-5, **overrides):
-    """Writes a synthetic model file. `shape` is a key of SHAPES or a dict with the same fields."""
+def write_gguf(path, shape, scheme, seed=1234, sigma=0.02, norm_random=False, eps=1e-5, embd_quant=False, **overrides):
+    """Writes a synthetic model file. `shape` is a key of SHAPES or a dict with the same fields.
+    embd_quant: token_embd is quantised like attn_q (what real checkpoints ship) instead of F32."""
     s = dict(SHAPES[shape]) if isinstance(shape, str) else dict(shape)
     s.update(overrides)
     cfg = _Cfg(s["hidden"], s["ffn"], s["n_heads"], s["n_kv_heads"], s["n_layers"], s["vocab"], s["max_pos"],
-               eps, s["theta"], scheme, int(norm_random), seed, sigma)
+               eps, s["theta"], scheme, int(bool(norm_random)) | (2 if embd_quant else 0), seed, sigma)
     rc = lib().b200_synth_write_gguf(os.fsencode(path), ctypes.byref(cfg))
     if rc:
         raise RuntimeError(f"b200_synth_write_gguf failed with status {rc}")
