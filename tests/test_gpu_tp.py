@@ -65,3 +65,70 @@ def test_tp2_matches_oracle(pkg, tmp_path, kv_i8, fused):
     for s in range(6):
         t0, t1 = int(orc.decode(t0, 13 + s, seq=0).argmax()), int(orc.decode(t1, 1 + s, seq=1).argmax())
         assert res[0][3][s].tolist() == [t0, t1]
+
+
+def _rank_batch(rank, world, path, id_q, out_q, kv_i8):
+    import __graft_entry__
+    pkg = __graft_entry__.load_package()
+    if rank == 0:
+        nid = pkg.api.nccl_unique_id()
+        for _ in range(world - 1):
+            id_q.put(nid)
+    else:
+        nid = id_q.get(timeout=120)
+    B = 16
+    eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if kv_i8 else pkg.KV_F32, max_seqs=B, device=rank, tp_rank=rank,
+                               tp_size=world, nccl_id=nid)
+    prompt = (np.arange(40, dtype=np.int32) * 37 + 5) % 1024
+    lg_prompt = eng.prefill(prompt, slot=0)          # 40 tokens: the tensor-core path, partial tiles summed by ncclAllReduce
+    toks = [int(lg_prompt.argmax())] + list(range(3, 3 + B - 1))
+    pos = [40] + [0] * (B - 1)
+    steps = []
+    for _ in range(2):                                 # batch 16: the tensor-core path under tensor parallelism
+        lg, am = eng.decode(toks, pos)
+        steps.append((lg.copy(), am.copy()))
+        toks, pos = [int(a) for a in am], [p + 1 for p in pos]
+    out_q.put((rank, lg_prompt, steps))
+    eng.close()
+
+
+@pytest.mark.parametrize("kv_i8", [False, True])
+def test_tp2_batch16_and_prompt_on_the_tensor_core_path(pkg, tmp_path, kv_i8):
+    """Two ranks, batch 16 and a 40-token prompt: column-split launches as on one GPU, row-split O / down launches
+    store partial [tokens, H] tiles that one ncclAllReduce per launch sums. Logits against the oracle: 2e-2 absolute
+    with an FP32 cache; with the INT8 cache the fp16 products that feed the cache quantizer put the bound at 1.5 % of
+    the largest logit (same rule as the single-GPU prompt tests)."""
+    if pkg.api.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import oracle_lib as ol
+    path = pkg.synth.write_gguf(str(tmp_path / "mha.gguf"), "tiny_mha", scheme=1, norm_random=True)
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_rank_batch, args=(r, 2, path, id_q, out_q, kv_i8)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted((out_q.get(timeout=300) for _ in procs), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    B = 16
+    orc = ol.OracleModel.from_gguf(path, kv_int8=kv_i8, max_seqs=B)
+    prompt = (np.arange(40, dtype=np.int32) * 37 + 5) % 1024
+    ref_p = orc.prefill(prompt, seq=0)
+
+    def tol(ref):
+        return max(2e-2, 1.5e-2 * float(np.abs(ref).max())) if kv_i8 else 2e-2
+
+    for r in range(2):
+        assert np.abs(res[r][1] - ref_p).max() <= tol(ref_p)
+    assert np.array_equal(res[0][1], res[1][1])       # both ranks hold the same gathered logits
+    toks = [int(res[0][1].argmax())] + list(range(3, 3 + B - 1))
+    pos = [40] + [0] * (B - 1)
+    for s in range(2):
+        lg, am = res[0][2][s]
+        assert np.array_equal(lg, res[1][2][s][0]) and np.array_equal(am, res[1][2][s][1])
+        for b in range(B):
+            ref = orc.decode(toks[b], pos[b], seq=b)
+            assert np.abs(lg[b] - ref).max() <= tol(ref), (s, b)
+        toks, pos = [int(a) for a in am], [p + 1 for p in pos]

@@ -393,11 +393,13 @@ static unsigned long long* trace_rec(const b200_engine* e, int launch_index) {
 }
 
 // Tensor parallel: sum the partial [batch, H] outputs over the ranks, then add them to the residual stream.
-static int tp_reduce_add(b200_engine* e, int batch, cudaStream_t st) {
+static int tp_reduce_add(b200_engine* e, int batch, cudaStream_t st, float* h = nullptr, float* partial = nullptr) {
   Nccl& n = Nccl::get();
   const size_t count = (size_t)batch * e->H;
-  n.check(n.AllReduce(e->d_partial, e->d_partial, count, Nccl::kFloat32, Nccl::kSum, e->nccl_comm, st), "ncclAllReduce");
-  add_inplace_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(e->d_h, e->d_partial, (int)count);
+  if (!h) h = e->d_h;
+  if (!partial) partial = e->d_partial;
+  n.check(n.AllReduce(partial, partial, count, Nccl::kFloat32, Nccl::kSum, e->nccl_comm, st), "ncclAllReduce");
+  add_inplace_kernel<<<(unsigned)std::min<size_t>((count + 255) / 256, 4096), 256, 0, st>>>(h, partial, count);
   CK(cudaGetLastError());
   return 2;
 }
@@ -425,7 +427,7 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
   const int ctas = (int)((p.seg[0].rows + TC_M - 1) / TC_M) * ((batch + TC_MAX_N - 1) / TC_MAX_N);
   const int nblk = p.K / 256;
   int ks = 1;
-  if (p.epi == EPI_RESID && p.nseg == 1 && batch <= 512 && e->d_tc_part) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
+  if ((p.epi == EPI_RESID || (p.epi == EPI_STORE && !p.amax_val)) && p.nseg == 1 && batch <= 512 && e->d_tc_part) ks = std::max(1, std::min({8, e->num_sms / std::max(1, ctas), nblk / 4}));
   if (ks > 1) {
     t.ksplit = ks; t.kblocks = (nblk + ks - 1) / ks;
     t.ksplit = (nblk + t.kblocks - 1) / t.kblocks;  // no empty split
@@ -433,14 +435,15 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
     launch_gemm_tc(e, t, st);
     const size_t nel = (size_t)batch * p.seg[0].rows;
     if (p.seg[0].rows % 4 || p.y_stride % 4) throw std::runtime_error("split-K matmul: rows must be a multiple of 4");
-    splitk_reduce_kernel<<<(unsigned)std::min<size_t>((nel / 4 + 255) / 256, 1184), 256, 0, st>>>(e->d_tc_part, t.ksplit, batch, p.seg[0].rows, p.resid, p.y, p.y_stride);
+    splitk_reduce_kernel<<<(unsigned)std::min<size_t>((nel / 4 + 255) / 256, 1184), 256, 0, st>>>(e->d_tc_part, t.ksplit, batch, p.seg[0].rows, p.resid, p.epi == EPI_RESID ? 1 : 0, p.y,
+                                                                                                   p.y_stride);
     CK(cudaGetLastError());
     ++n;
   } else {
     launch_gemm_tc(e, t, st);
   }
   if (p.amax_val) {  // lm_head: the matvec kernel leaves argmax partials; here a small kernel scans the logits
-    argmax_rows_kernel<<<batch, 256, 0, st>>>(p.y, p.y_stride, p.amax_val, p.amax_idx);
+    argmax_rows_kernel<<<batch, 256, 0, st>>>(p.y, p.y_stride, p.amax_row_offset, p.amax_val, p.amax_idx);
     CK(cudaGetLastError());
     if (grid_out) *grid_out = 1;
     ++n;
@@ -462,22 +465,18 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   // and the next matvec adds the tp slots to the residual stream in its prologue and stores the
   // new stream to the other of two buffers. There are 2L exchanges per step, so the stream is back
   // in d_h when the step ends.
-  const bool peer = tp && e->use_peer;
-  const bool use_tc = !tp && batch >= e->gemm_min_batch;
-  const size_t slots_bytes = (size_t)2 * e->tp_size * e->max_seqs * H * sizeof(float);
+  const bool use_tc = batch >= e->gemm_min_batch;  // under tensor parallelism the partial [batch, H] tiles go through ncclAllReduce
+  const bool peer = tp && e->use_peer && !use_tc;
   auto slot_of = [&](void* region, int k, int src) {
-    return static_cast<float*>(region) + ((size_t)(k & 1) * e->tp_size + src) * e->max_seqs * H;
-  };
-  auto flag_of = [&](void* region, int k, int src) {
-    return reinterpret_cast<unsigned*>(static_cast<uint8_t*>(region) + slots_bytes) + (k & 1) * e->tp_size + src;
+    return static_cast<uint2*>(region) + ((size_t)(k & 1) * e->tp_size + src) * e->max_seqs * H;
   };
   float* hcur = e->d_h;
   float* hnext = e->d_h2;
   int pending = -1;  // exchange whose sum the next matvec has to pick up
   auto as_producer = [&](GemvParams& p, int k) {
     p.epi = EPI_PEER; p.tp = e->tp_size; p.tp_rank = e->tp_rank; p.y = nullptr; p.y_stride = H;
-    for (int r = 0; r < e->tp_size; ++r) { p.peer_y[r] = slot_of(e->peer_region[r], k, e->tp_rank); p.peer_flag[r] = flag_of(e->peer_region[r], k, e->tp_rank); }
-    p.peer_ticket = e->d_peer_ticket; p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)k + 1u;
+    for (int r = 0; r < e->tp_size; ++r) p.peer_y[r] = slot_of(e->peer_region[r], k, e->tp_rank);
+    p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)k + 1u;
     pending = k;
   };
   auto as_consumer = [&](GemvParams& p) {
@@ -485,7 +484,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     if (pending < 0) return;
     p.tp = e->tp_size; p.tp_rank = e->tp_rank;
     p.x_parts = slot_of(e->xregion, pending, 0); p.parts_stride = (size_t)e->max_seqs * H;
-    p.wait_flags = flag_of(e->xregion, pending, 0); p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)pending + 1u;
+    p.epoch_base = e->d_epoch; p.epoch_k = (unsigned)pending + 1u;
     p.x_out = hnext;
     std::swap(hcur, hnext);
     pending = -1;
@@ -590,7 +589,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid * e->tp_size; s.parts_per_rank = grid; s.batch = batch;
     s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
     s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
-    if (peer) { s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L; }
+    if (peer) { s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L; }  // the next step's packets carry new numbers
     select_kernel<<<1, 256, 0, st>>>(s);
     CK(cudaGetLastError());
     ++launches;
@@ -618,6 +617,7 @@ static void ensure_prefill_buffers(b200_engine* e) {
   e->pf_attn = dev_alloc<float>(e, (size_t)T * e->H);
   e->pf_act = dev_alloc<float>(e, (size_t)T * e->F);
   e->pf_x16 = dev_alloc<uint16_t>(e, (size_t)T * std::max(e->H, e->F));
+  if (e->tp_size > 1) e->pf_partial = dev_alloc<float>(e, (size_t)T * e->H);
   size_t items = 0;
   for (int t = 1; t <= T; ++t) items = std::max(items, (size_t)t * e->nq * attn_nsplit(e, t));
   e->pf_part_o = dev_alloc<float>(e, items * e->hd);
@@ -633,6 +633,7 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
   ensure_prefill_buffers(e);
   cudaStream_t st = e->stream;
   const int H = e->H, F = e->F, KVD = e->KVD;
+  const bool tp = e->tp_size > 1;
   std::vector<int> meta((size_t)3 * T);
   for (int t = 0; t < T; ++t) { meta[t] = ids[t]; meta[T + t] = start + t; meta[2 * T + t] = slot; }
   CK(cudaMemcpyAsync(e->pf_ints, meta.data(), meta.size() * 4, cudaMemcpyHostToDevice, st));
@@ -678,9 +679,10 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
     }
     {
       GemvParams p{};
-      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->pf_attn; p.x_stride = e->Hq; p.epi = EPI_RESID;
-      p.y = e->pf_h; p.y_stride = H;
+      p.seg[0] = seg_of(w.wo); p.nseg = 1; p.K = e->Hq; p.x = e->pf_attn; p.x_stride = e->Hq; p.epi = tp ? EPI_STORE : EPI_RESID;
+      p.y = tp ? e->pf_partial : e->pf_h; p.y_stride = H;
       launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+      if (tp) tp_reduce_add(e, T, st, e->pf_h, e->pf_partial);
     }
     {
       GemvParams p{};
@@ -691,16 +693,21 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
     }
     {
       GemvParams p{};
-      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->pf_act; p.x_stride = F; p.epi = EPI_RESID;
-      p.y = e->pf_h; p.y_stride = H;
+      p.seg[0] = seg_of(w.wdown); p.nseg = 1; p.K = F; p.x = e->pf_act; p.x_stride = F; p.epi = tp ? EPI_STORE : EPI_RESID;
+      p.y = tp ? e->pf_partial : e->pf_h; p.y_stride = H;
       launch_linear(e, p, T, st, true, nullptr, e->pf_x16);
+      if (tp) tp_reduce_add(e, T, st, e->pf_h, e->pf_partial);
     }
   }
   if (last) {  // final norm + lm_head for the last token only, on the matvec kernel
     GemvParams p{};
     p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->pf_h + (size_t)(T - 1) * H; p.x_stride = H;
-    p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE; p.y = e->d_logits; p.y_stride = e->V;
+    p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE; p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
     launch_gemv(e, p, 1, st);
+    if (tp) {  // every rank holds its share of the vocabulary: gather the shares (in rank order = vocabulary order for one row)
+      Nccl& n = Nccl::get();
+      n.check(n.AllGather(e->d_logits_local, e->d_logits, (size_t)e->Vl, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
+    }
   }
 }
 

@@ -55,12 +55,11 @@ struct b200_engine {
   int* d_error = nullptr;       // device alias of h_error
   int* h_error = nullptr;       // host-mapped word a kernel sets when a bounded wait gives up
   // one-shot all-reduce over peer memory (tensor parallelism): an IPC-shared region per rank holding the
-  // exchange slots [2][tp][max_seqs][H] and their flag words [2][tp]
+  // exchange slots [2][tp][max_seqs][H] of 8-byte packets {value, exchange number}
   bool use_peer = false;
   void* xregion = nullptr;
   void* peer_region[8] = {nullptr};  // the same region of every rank, mapped here (own rank: xregion)
   unsigned* d_epoch = nullptr;
-  unsigned* d_peer_ticket = nullptr;
   float* d_h2 = nullptr;             // second residual-stream buffer (the consumer of an exchange writes the other one)
   unsigned long long* d_trace = nullptr;  // B200_TRACE=1: one 8-slot timestamp record per launch of a step
   int trace_cap = 0;
@@ -96,6 +95,7 @@ struct b200_engine {
   float* pf_attn = nullptr;
   float* pf_act = nullptr;
   void* pf_x16 = nullptr;
+  float* pf_partial = nullptr;   // tensor parallel: partial [chunk][H] outputs awaiting the all-reduce
   float* pf_part_o = nullptr;
   float* pf_part_ml = nullptr;
   int* pf_tickets = nullptr;

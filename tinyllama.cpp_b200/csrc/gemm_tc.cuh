@@ -512,15 +512,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcParams p
   if (warp == 0) tc_dealloc(tmem_d, p.tmem_cols);
 }
 
-// Split-K epilogue: y[t][r] = (resid ? resid : y)[t][r] + sum_z part[z][t][r], z in order (deterministic).
+// Split-K epilogue: y[t][r] = base + sum_z part[z][t][r], z in order (deterministic); base = (resid ? resid : y)[t][r]
+// when add_base is set, else 0.
 // Four consecutive rows per thread (the launcher checks that rows and y_stride are multiples of 4).
-__global__ void splitk_reduce_kernel(const float* __restrict__ part, int ksplit, int T, int rows, const float* __restrict__ resid,
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int ksplit, int T, int rows, const float* __restrict__ resid, int add_base,
                                      float* __restrict__ y, int y_stride) {
   const size_t n = (size_t)T * rows, n4 = n / 4;
   const int rows4 = rows / 4;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / rows4, r = (i - t * rows4) * 4;
-    float4 acc = *reinterpret_cast<const float4*>((resid ? resid : y) + t * y_stride + r);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (add_base) acc = *reinterpret_cast<const float4*>((resid ? resid : y) + t * y_stride + r);
     for (int z = 0; z < ksplit; ++z) {
       const float4 v = __ldcs(reinterpret_cast<const float4*>(part + (size_t)z * n) + i);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;

@@ -169,21 +169,20 @@ struct GemvParams {
   unsigned long long* trace;  // optional step-trace record, eight slots: 0 entry, 1-3 dependency wait over, 4 input vector held,
                               // 5 prologue done, 6 first tile computed, 7 end
   // ---- tensor-parallel exchange without a collective call (one-shot all-reduce over peer memory) ----
-  // Producer side (EPI_PEER): the partial output rows are stored into the exchange buffer of every
-  // rank (peer_y[r]: [batch][y_stride] slot of this rank in rank r's memory); the last CTA to finish
-  // then publishes the exchange number in every rank's flag word (peer_flag[r]).
+  // Every exchanged value travels as an 8-byte packet {value, exchange number}: one aligned 64-bit
+  // store, so the number can never be seen without its value, and no flag word, ticket or
+  // system-wide fence is needed.
+  // Producer side (EPI_PEER): each partial output row is stored as a packet into this rank's slot of
+  // the exchange buffer of every rank (peer_y[r]: [batch][y_stride] packets in rank r's memory).
   // Consumer side (x_parts != nullptr): the input vector is x + the tp slots of the local exchange
-  // buffer, summed in rank order; the kernel first waits (bounded) until every rank's flag has
-  // reached this exchange's number, and its first CTA stores the sum to x_out.
+  // buffer, summed in rank order; each thread polls (bounded) the packets it needs until they carry
+  // this exchange's number. The first CTA stores the sum to x_out.
   int tp, tp_rank;
-  float* peer_y[GEMV_MAX_TP];
-  unsigned* peer_flag[GEMV_MAX_TP];
-  unsigned* peer_ticket;        // CTAs of this launch that have stored their rows (returns to 0)
+  uint2* peer_y[GEMV_MAX_TP];
   const unsigned* epoch_base;   // device scalar: exchanges completed before this step
   unsigned epoch_k;             // 1 + index of this launch's exchange within the step
-  const float* x_parts;         // [tp][parts_stride] local exchange slots to add to x
-  size_t parts_stride;
-  const unsigned* wait_flags;   // [tp] local flag words of that exchange buffer
+  const uint2* x_parts;         // [tp][parts_stride] local exchange slots (packets) to add to x
+  size_t parts_stride;          // packets between the slots of consecutive ranks
   float* x_out;                 // [batch][x_stride] where CTA 0 stores the summed input
 };
 
@@ -638,6 +637,7 @@ struct GemvShared {
   float sv[GEMV_WARPS];
   int si[GEMV_WARPS];
   int abort_flag;
+  int xfail;  // a poll of the tensor-parallel exchange gave up
 };
 
 __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
@@ -648,6 +648,7 @@ __device__ __forceinline__ void pipe_init(GemvShared* sh, int nstages) {
     }
     mbar_init(&sh->xready_bar, GEMV_WARPS);
     sh->abort_flag = 0;
+    sh->xfail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -689,7 +690,7 @@ __device__ __forceinline__ void gemv_produce(const GemvParams& prm, GemvShared* 
 // Finishes the rows of the n tiles parked in sh->part (tiles first_i .. first_i+n-1 of this CTA's
 // sequence): every thread sums the partials of one row in warp order and applies the epilogue.
 __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh, int first_i, int n, int bidx, int cta, int ncta,
-                                        float& best_v, int& best_i) {
+                                        unsigned peer_tag, float& best_v, int& best_i) {
   consumer_sync();
   const int tid = threadIdx.x, lane = tid & 31;
   const int R = prm.R, S = prm.S;
@@ -723,7 +724,8 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
       if (valid) {
         const int row = irow;
         if (prm.epi == EPI_PEER) {
-          for (int r = 0; r < prm.tp; ++r) prm.peer_y[r][(size_t)bidx * prm.y_stride + row] = tot;
+          const uint2 pkt = make_uint2(__float_as_uint(tot), peer_tag);
+          for (int r = 0; r < prm.tp; ++r) prm.peer_y[r][(size_t)bidx * prm.y_stride + row] = pkt;
         } else if (prm.epi == EPI_RESID) {
           const float* rs = (prm.resid ? prm.resid : prm.y) + (size_t)bidx * prm.y_stride + row;
           prm.y[(size_t)bidx * prm.y_stride + row] = *rs + tot;
@@ -763,6 +765,7 @@ struct ConsumerCtx {
   int rg, bi;      // this warp's row group and block within a stage
   bool rg_ok, breg;
   int cur_type;    // block type the register-held B fragments were built for
+  unsigned peer_tag;  // exchange number carried by the packets of an EPI_PEER launch
   float best_v;
   int best_i;
 };
@@ -825,7 +828,7 @@ __device__ __forceinline__ void gemv_tiles(const GemvParams& prm, const GemvSeg&
       sh->part[pp][warp][L.g + 8] = acc1;
     }
     // rows are finished when GEMV_NTB tiles are parked or after the CTA's last tile
-    if (pp == GEMV_NTB - 1 || c.tile + c.ncta >= prm.ntiles) gemv_flush(prm, sh, c.i - pp, pp + 1, c.bidx, c.cta, c.ncta, c.best_v, c.best_i);
+    if (pp == GEMV_NTB - 1 || c.tile + c.ncta >= prm.ntiles) gemv_flush(prm, sh, c.i - pp, pp + 1, c.bidx, c.cta, c.ncta, c.peer_tag, c.best_v, c.best_i);
   }
 }
 
@@ -853,23 +856,42 @@ __device__ __forceinline__ void gemv_store_argmax(const GemvParams& prm, GemvSha
 
 __host__ __device__ __forceinline__ size_t gemv_ring_offset(int K, int P) { return (act_smem_bytes(K, P) + 127) / 128 * 128; }
 
-// Loads eight elements of the input vector; under tensor parallelism adds the ranks' partial sums
-// (in rank order, so every rank computes the same bits) and lets the first CTA store the total.
+// Loads eight elements of the input vector. Under tensor parallelism it adds the ranks' partial
+// sums, in rank order (so every rank computes the same bits): the eight packets of each rank are
+// polled until all carry this exchange's number (written by other GPUs: read past L1), bounded; the
+// first CTA stores the total.
 struct XLoad {
   const float* x;
-  const float* parts;  // nullptr: plain load
+  const uint2* parts;  // nullptr: plain load
   size_t parts_stride;
   int nparts;
+  unsigned tag;
   float* out;          // nullptr: do not store
+  int* fail;           // set when a poll gives up
   __device__ __forceinline__ void operator()(int e, float (&v)[8]) const {
     const float4 a = *reinterpret_cast<const float4*>(x + e), b = *reinterpret_cast<const float4*>(x + e + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     if (parts) {
 #pragma unroll 1
-      for (int r = 0; r < nparts; ++r) {  // written by other GPUs: read past L1
-        const float4 c = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)r * parts_stride + e));
-        const float4 d = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)r * parts_stride + e + 4));
-        v[0] += c.x; v[1] += c.y; v[2] += c.z; v[3] += c.w; v[4] += d.x; v[5] += d.y; v[6] += d.z; v[7] += d.w;
+      for (int r = 0; r < nparts; ++r) {
+        const uint2* src = parts + (size_t)r * parts_stride + e;
+        uint4 p[4];
+        int it = 0;
+        while (true) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p[i].x), "=r"(p[i].y), "=r"(p[i].z), "=r"(p[i].w) : "l"(src + 2 * i));
+          const bool ok = p[0].y == tag && p[0].w == tag && p[1].y == tag && p[1].w == tag && p[2].y == tag && p[2].w == tag && p[3].y == tag &&
+                          p[3].w == tag;
+          if (ok) break;
+          if (++it > (1 << 22)) {  // bounded (seconds): report instead of hanging when a rank has gone away
+            *reinterpret_cast<volatile int*>(fail) = 1;
+            break;
+          }
+          if (it > 16) __nanosleep(32);
+        }
+        v[0] += __uint_as_float(p[0].x); v[1] += __uint_as_float(p[0].z); v[2] += __uint_as_float(p[1].x); v[3] += __uint_as_float(p[1].z);
+        v[4] += __uint_as_float(p[2].x); v[5] += __uint_as_float(p[2].z); v[6] += __uint_as_float(p[3].x); v[7] += __uint_as_float(p[3].z);
       }
       if (out) {
         *reinterpret_cast<float4*>(out + e) = make_float4(v[0], v[1], v[2], v[3]);
@@ -886,7 +908,8 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* 
   const int cta = blockIdx.x, ncta = gridDim.x, bidx = blockIdx.y;
   unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
   XLoad xfn{prm.x + (size_t)bidx * prm.x_stride, prm.x_parts ? prm.x_parts + (size_t)bidx * prm.x_stride : nullptr,
-            prm.parts_stride, prm.tp, (prm.x_out && cta == 0) ? prm.x_out + (size_t)bidx * prm.x_stride : nullptr};
+            prm.parts_stride, prm.tp, prm.x_parts ? *prm.epoch_base + prm.epoch_k : 0u,
+            (prm.x_out && cta == 0) ? prm.x_out + (size_t)bidx * prm.x_stride : nullptr, &sh->xfail};
   auto after_x = [&](float ss) {
     uint32_t z;
     asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(__float_as_int(ss)));  // issue order: after the loads have returned
@@ -900,24 +923,9 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* 
     trace_stamp(rec, 1);
     trace_stamp(rec, 2);
     trace_stamp(rec, 3);
-    if (prm.wait_flags) {  // tensor parallel: the other ranks' partial sums must have landed in this GPU's memory
-      if ((int)threadIdx.x < prm.tp && (int)threadIdx.x != prm.tp_rank) {
-        const unsigned want = *prm.epoch_base + prm.epoch_k;
-        const volatile unsigned* f = prm.wait_flags + threadIdx.x;
-        int it = 0;
-        while ((int)(*f - want) < 0) {
-          if (++it > (1 << 24)) {  // bounded (seconds): report instead of hanging when a rank has gone away
-            pipe_fail(prm, sh);
-            break;
-          }
-          __nanosleep(100);
-        }
-        __threadfence_system();
-      }
-      consumer_sync();
-    }
   };
   act_build<P>(smem, xfn, prm.norm_w, prm.eps, prm.K, sh->red, before_x, after_x);
+  if (prm.x_parts && threadIdx.x == 0 && *(volatile int*)&sh->xfail) pipe_fail(prm, sh);  // act_build ended with a barrier: every poll is over
   trace_stamp(rec, 5);
   const ActImage a = act_carve(smem, prm.K, P);
 
@@ -936,6 +944,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* 
   c.breg = prm.nslab == 1;
   c.cur_type = -1;
   c.best_v = -INFINITY; c.best_i = 0x7fffffff;
+  c.peer_tag = prm.epi == EPI_PEER ? *prm.epoch_base + prm.epoch_k : 0u;
   BFrag bf;
   int seg_end = 0;
 #pragma unroll 1
@@ -968,18 +977,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const __grid_cons
   unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
   trace_stamp(rec, 0);
   gemv_consume<P>(prm, &sh, smem, ring, nstages);
-  if (prm.epi == EPI_PEER && threadIdx.x == 0) {
-    // every thread's stores were issued before the barrier that ends the last flush; make them
-    // visible system-wide, and let the last CTA of the launch publish the exchange number
-    __threadfence_system();
-    if (atomicAdd(prm.peer_ticket, 1u) == gridDim.x * gridDim.y - 1) {
-      atomicExch(prm.peer_ticket, 0u);
-      __threadfence_system();
-      const unsigned ep = *prm.epoch_base + prm.epoch_k;
-      for (int r = 0; r < prm.tp; ++r)
-        if (r != prm.tp_rank) *reinterpret_cast<volatile unsigned*>(prm.peer_flag[r]) = ep;
-    }
-  }
   trace_stamp(rec, 7);
 }
 

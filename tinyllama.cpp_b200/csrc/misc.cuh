@@ -76,7 +76,8 @@ __global__ void select_kernel(const SelectParams p) {
 
 // First maximum of each row of logits [batch][vocab] (reference api.cpp:134-136), in the partial
 // format select_kernel merges (one part per sequence). One block per sequence.
-__global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ amax_val, int* __restrict__ amax_idx) {
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, int index_offset, float* __restrict__ amax_val,
+                                   int* __restrict__ amax_idx) {
   __shared__ float sv[32];
   __shared__ int si[32];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -100,14 +101,13 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, 
     for (int w = 1; w < nwarps; ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
     amax_val[b] = bv;
-    amax_idx[b] = bi;
+    amax_idx[b] = bi + index_offset;  // offset of this rank's share of the vocabulary
   }
 }
 
 // h[i] += partial[i]: the residual add after a tensor-parallel all-reduce.
-__global__ void add_inplace_kernel(float* __restrict__ h, const float* __restrict__ partial, int n) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) h[i] = h[i] + partial[i];
+__global__ void add_inplace_kernel(float* __restrict__ h, const float* __restrict__ partial, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) h[i] = h[i] + partial[i];
 }
 
 // fp16 -> fp32, element by element (op-level checks of the batch RMSNorm path).
