@@ -44,13 +44,15 @@ METRIC = "decode tokens/s (Llama-2-7B Q4_K_M, bs=1) and % of HBM roofline at 1/2
 
 
 def peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, source): the driver-measured figures when present, else the pool's fallback."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return float(json.load(open(p))["hbm_gbs"]), "measured"
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -191,13 +193,14 @@ def parity_in_run(eng, shape, scheme, kv):
         tok = int(ids[i + 1])
     return {"case": tag, "source": "tests/golden/full_models.npz: " + ("restated oracle (INT8 KV)" if tag.endswith("i8") else "reference CPU path"),
             "ids_checked": len(ids), "ids_match": got == [int(v) for v in ids], "max_abs_logit_err": round(err, 6),
-            "logit_gate": 2e-2}
+            "logit_gate": 2e-2 if not tag.endswith("i8") else round(max(2e-2, 0.25 * float(np.abs(g[f"{tag}_prefill_logits"] - g[f"{case}_f32_prefill_logits"]).max())), 4),
+            "logit_gate_note": None if not tag.endswith("i8") else "INT8 cache: 2e-2 or a quarter of the oracle's own INT8-vs-FP32 drift (rounding flips of cached values)"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=None, help="timed decode steps (default 256; 96 for the 70B workloads, whose context ends at the reference's 8192-position cap)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -206,11 +209,17 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the in-run parity check against the golden fixtures")
     args = ap.parse_args()
     shape, scheme, batch, prompt_len, kv = WORKLOADS[args.workload]
+    if args.steps is None:
+        args.steps = 96 if shape == "llama2-70b" else 256
     if args.impl == "reference":
         return run_reference(args, shape, scheme, batch, prompt_len, kv)
 
     rank, local_rank, world = dist_env()
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
+    # stdout carries the one JSON line only: whatever a library prints while the run lasts (NCCL's version banner,
+    # for one) goes to stderr, and the line is written to the saved descriptor at the end
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     warmup = max(args.warmup, 3)
     pkg = __graft_entry__.load_package()
     dist = None
@@ -234,8 +243,13 @@ def main():
             idt.copy_(torch.tensor(list(pkg.api.nccl_unique_id()), dtype=torch.uint8))
         dist.broadcast(idt, src=0)
         nccl_id = bytes(idt.cpu().tolist())
+    max_pos = pkg.synth.SHAPES[shape]["max_pos"]
+    longest = max(prompt_lengths(batch, prompt_len))
+    e2e_steps = max(1, min(args.steps, 64, max_pos - longest - warmup - args.steps - 2))
+    if longest + warmup + args.steps + 1 + e2e_steps > max_pos:
+        raise SystemExit(f"{args.workload}: prompt {longest} + {warmup} + {args.steps} steps exceed the model's {max_pos} positions")
     eng = pkg.Engine.from_gguf(path, kv_dtype=pkg.KV_I8 if kv == "i8" else pkg.KV_F32, max_seqs=batch,
-                               max_ctx=max(prompt_lengths(batch, prompt_len)) + args.steps + warmup + 80, act_planes=args.planes, device=local_rank,
+                               max_ctx=min(max_pos, longest + args.steps + warmup + e2e_steps + 8), act_planes=args.planes, device=local_rank,
                                tp_rank=rank, tp_size=world, nccl_id=nccl_id)
     t_load = time.perf_counter() - t_load
     vocab = eng.vocab
@@ -270,7 +284,6 @@ def main():
     tokens_per_s = batch * args.steps / (ms / 1000.0)  # one tensor-parallel group: the ranks share the same sequences
 
     # ---- end to end through the C ABI with host buffers: token ids in, logits out, host argmax ----
-    e2e_steps = min(args.steps, 64)
     toks = out[-1].copy()
     eng.decode(toks, at(pos))  # graph already warm; one untimed call
     pos += 1
@@ -285,14 +298,25 @@ def main():
     st = eng.stats()
     L = eng.desc.num_hidden_layers
     kinds = {"gate_up_swiglu": (0, L), "qkv_rope": (1, L), "o_proj": (2, L), "down_proj": (3, L), "lm_head": (4, 1)}
-    peak, peak_src = peaks()
-    ksum_b = ksum_t = 0.0
+    peak, peak_tf, peak_src = peaks()
+    ksum_b = ksum_t = ksum_f = 0.0
     kern = {}
+    on_tc = batch >= 16  # the step's linear layers run on the tensor-core matmul: time that path, for the whole batch
+    d = eng.desc
+    hd = d.hidden_size // d.num_attention_heads
+    rows_of = {"gate_up_swiglu": 2 * d.intermediate_size // world, "qkv_rope": (d.num_attention_heads + 2 * d.num_key_value_heads) * hd // world,
+               "o_proj": d.hidden_size, "down_proj": d.hidden_size, "lm_head": d.vocab_size // world}
+    k_of = {"gate_up_swiglu": d.hidden_size, "qkv_rope": d.hidden_size, "o_proj": d.hidden_size // world,
+            "down_proj": d.intermediate_size // world, "lm_head": d.hidden_size}
     for name, (which, per_step) in kinds.items():
-        us, nbytes = eng.time_kernel(which, max(2 * L, 32))
+        us, nbytes = eng.time_kernel(which + (16 if on_tc else 0), max(2 * L, 32))
+        flops = 2.0 * rows_of[name] * k_of[name] * batch
         kern[name] = {"us": round(us, 3), "bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1), "launches_per_step": per_step}
+        if on_tc:
+            kern[name]["TFLOPs"] = round(flops / us / 1e6, 1)
         ksum_b += nbytes * per_step
         ksum_t += us * per_step
+        ksum_f += flops * per_step
     gemv_launches = sum(v[1] for v in kinds.values())
     # DRAM bytes (read + write) per launch from one ncu capture of this workload's four per-layer kinds
     # (profiles/gemv_kernel_7b_q4km_bs1.txt); the lm_head launch was not captured and is scaled from its
@@ -311,11 +335,21 @@ def main():
     step_gbps = step_bytes / (ms / args.steps / 1e3) / 1e9 / world  # per GPU
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "traffic": traffic, "traffic_source": traffic_source, "peak_source": peak_src, "kernel": f"gemv_kernel<{args.planes}>",
+                "timed": "each kind alone, stream-ordered launches without programmatic overlap, a different layer's weights per launch",
                 "bytes_per_launch": int(ksum_b / gemv_launches), "us_per_launch": round(ksum_t / gemv_launches, 3),
                 "kinds": kern, "step_bytes": int(step_bytes), "step_GBps": round(step_gbps, 1),
                 "step_frac_of_measured_peak": round(step_gbps / peak, 4), "step_frac_of_8TBps": round(step_gbps / 8000.0, 4)}
 
     clocks = sampler.finish()
+    if on_tc:
+        # batch >= 16: the linear layers run on the tcgen05 matmul (with its fp16 conversion and split-K reduction). Below
+        # ~128 tokens the matmul is still bound by the packed weight bytes (2 * batch / 0.5625 FLOP per byte against a
+        # machine balance of ~250), so the roofline stays the HBM one; the tensor throughput is reported beside it.
+        tf = ksum_f / ksum_t / 1e6
+        roofline.update({"kernel": "gemm_tc_kernel (+ to_half_kernel, splitk_reduce_kernel)", "traffic": None, "traffic_source": None,
+                         "tensor_TFLOPs": round(tf, 1), "tensor_peak_TFLOPs": peak_tf, "tensor_frac": round(tf / peak_tf, 4)})
+        if batch >= 128:
+            roofline.update({"bound": "tensor", "achieved": round(tf, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4)})
     line = {"metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": f"i{8 * args.planes} activations x packed int weights, f32 accumulate",
@@ -341,7 +375,7 @@ def main():
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference",
                                 "sample": f"{n} decode steps of the same model file from an empty context, {dt:.1f} s"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist:
         dist.destroy_process_group()
 

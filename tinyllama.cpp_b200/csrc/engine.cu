@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <thread>
 
 #include "attn.cuh"
 #include "attn_cluster.cuh"
@@ -26,6 +27,19 @@ static T* dev_alloc(b200_engine* e, size_t n) {
   CK(cudaMalloc(&p, std::max<size_t>(n * sizeof(T), 16)));
   if (e) e->allocations.push_back(p);
   return static_cast<T*>(p);
+}
+
+// memcpy split over a few threads: one thread moves 5-8 GB/s out of the page cache, which is less than the link takes.
+static void parallel_memcpy(void* dst, const void* src, size_t n) {
+  const int nt = n >= ((size_t)8 << 20) ? 4 : 1;
+  if (nt == 1) { std::memcpy(dst, src, n); return; }
+  std::thread th[4];
+  const size_t per = (n / nt + 4095) & ~(size_t)4095;
+  for (int i = 0; i < nt; ++i) {
+    const size_t off = std::min(n, per * i), len = std::min(per, n - off);
+    th[i] = std::thread([=] { if (len) std::memcpy(static_cast<uint8_t*>(dst) + off, static_cast<const uint8_t*>(src) + off, len); });
+  }
+  for (int i = 0; i < nt; ++i) th[i].join();
 }
 
 // cuTensorMapEncodeTiled, fetched from the driver at run time (the library links only the runtime).
@@ -124,6 +138,62 @@ static void launch_gqa_attention(const GqaAttnParams& a, int batch, bool kv_i8, 
   CK(cudaGetLastError());
 }
 
+// Device scratch of the loader, grown on demand and reused from tensor to tensor (stream order keeps the reuse safe
+// as long as every load-time kernel and copy runs on the same stream).
+static uint8_t* stage_scratch(b200_engine* e, int which, size_t bytes) {
+  auto& st = e->stage;
+  if (st.scratch_cap[which] < bytes) {
+    if (st.scratch[which]) {
+      CK(cudaDeviceSynchronize());  // earlier tensors may still be reading the old buffer
+      CK(cudaFree(st.scratch[which]));
+      st.scratch[which] = nullptr;
+      st.scratch_cap[which] = 0;
+    }
+    const size_t cap = std::max(bytes, (size_t)32 << 20);
+    CK(cudaMalloc((void**)&st.scratch[which], cap));
+    st.scratch_cap[which] = cap;
+  }
+  return st.scratch[which];
+}
+
+// Host (pageable, typically the mmap of the model file) -> device through two pinned buffers: while the copy engine
+// moves one chunk, the host fills the other. Replaces the reference's per-tensor host copy + upload
+// (weight_management.cpp:873-875).
+static void h2d_staged(b200_engine* e, void* dst, const void* src, size_t bytes, cudaStream_t stream) {
+  auto& st = e->stage;
+  if (!st.pinned[0]) {
+    st.chunk = (size_t)64 << 20;
+    for (int i = 0; i < 2; ++i) {
+      CK(cudaMallocHost((void**)&st.pinned[i], st.chunk));
+      CK(cudaEventCreateWithFlags(&st.done[i], cudaEventDisableTiming));
+    }
+  }
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  uint8_t* d = static_cast<uint8_t*>(dst);
+  for (size_t off = 0; off < bytes; off += st.chunk) {
+    const size_t n = std::min(st.chunk, bytes - off);
+    const int b = st.next;
+    st.next ^= 1;
+    CK(cudaEventSynchronize(st.done[b]));  // the copy that last used this buffer has finished (no-op the first time)
+    parallel_memcpy(st.pinned[b], s + off, n);
+    CK(cudaMemcpyAsync(d + off, st.pinned[b], n, cudaMemcpyHostToDevice, stream));
+    CK(cudaEventRecord(st.done[b], stream));
+  }
+}
+
+static void stage_release(b200_engine* e) {
+  auto& st = e->stage;
+  for (int i = 0; i < 2; ++i) {
+    if (st.pinned[i]) cudaFreeHost(st.pinned[i]);
+    if (st.done[i]) cudaEventDestroy(st.done[i]);
+    st.pinned[i] = nullptr; st.done[i] = nullptr;
+  }
+  for (int i = 0; i < 3; ++i) {
+    if (st.scratch[i]) cudaFree(st.scratch[i]);
+    st.scratch[i] = nullptr; st.scratch_cap[i] = 0;
+  }
+}
+
 // Uploads one packed tensor and lays it out on the device as the stage images the matvec kernel
 // streams (Q6_K / Q8_0 are first regrouped into aligned 256-element units). half >= 0: the tensor
 // is the gate (0) or up (1) projection and shares its image with the other one, every 16-row
@@ -156,18 +226,16 @@ static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* ho
   }
   t.bytes += bytes;
   if (half >= 0) t.halves |= 1 << half;
-  uint8_t* raw = nullptr;
-  uint8_t* units = nullptr;
-  uint16_t* dsrc = nullptr;
-  CK(cudaMalloc((void**)&raw, bytes + 16));
-  CK(cudaMemcpyAsync(raw, host, bytes, cudaMemcpyHostToDevice, stream));
+  uint8_t* raw = stage_scratch(e, 0, bytes + 16);
+  h2d_staged(e, raw, host, bytes, stream);
   const size_t n256 = (size_t)(rows * cols / 256);
   const uint8_t* usrc = raw;
+  uint16_t* dsrc = nullptr;
   if (type == T_Q6_K || type == T_Q8_0) {
-    CK(cudaMalloc((void**)&units, n256 * g.ub + 16));
+    uint8_t* units = stage_scratch(e, 1, n256 * g.ub + 16);
     const unsigned grid = (unsigned)((bytes + 255) / 256);
     if (type == T_Q6_K) {
-      CK(cudaMalloc((void**)&dsrc, n256 * 2 + 16));
+      dsrc = reinterpret_cast<uint16_t*>(stage_scratch(e, 2, n256 * 2 + 16));
       split_q6_k_kernel<<<grid, 256, 0, stream>>>(raw, nblk, units, reinterpret_cast<uint8_t*>(dsrc));
     } else {
       regroup_q8_0_kernel<<<grid, 256, 0, stream>>>(raw, nblk, units);
@@ -177,10 +245,7 @@ static void upload_packed(b200_engine* e, DevTensor& t, int type, const void* ho
   }
   stage_image_kernel<<<1184, 256, 0, stream>>>(usrc, dsrc, rows, g, half, t.base);
   CK(cudaGetLastError());
-  CK(cudaStreamSynchronize(stream));
-  CK(cudaFree(raw));
-  if (units) CK(cudaFree(units));
-  if (dsrc) CK(cudaFree(dsrc));
+  // no synchronisation here: the scratch buffers are reused by the next tensor on the same stream, in order
 }
 
 static GemvSeg seg_of(const DevTensor& t) {

@@ -115,4 +115,15 @@ struct b200_engine {
   int64_t weight_bytes = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<void*> allocations;
+  // Load-time staging: host bytes reach the device through two pinned buffers (the copy of one chunk
+  // overlaps the host-side memcpy of the next) into device scratch that is reused from tensor to tensor;
+  // everything here is released when the engine is finalized.
+  struct Staging {
+    uint8_t* pinned[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    size_t chunk = 0;
+    int next = 0;
+    uint8_t* scratch[3] = {nullptr, nullptr, nullptr};  // raw blocks, regrouped units, fp16 scale plane
+    size_t scratch_cap[3] = {0, 0, 0};
+  } stage;
 };
