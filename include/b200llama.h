@@ -193,6 +193,12 @@ int b200_engine_read_trace(b200_engine* e, uint64_t* out, int max_records, int* 
  * file) and keeps its shard: attn_q/k/v, ffn_gate/up and output by rows, attn_output and ffn_down by
  * 256-element blocks of the input dimension; two all-reduces per layer plus a gather of the logits.
  * All ranks must make the same calls with the same arguments. ---- */
+/* Self-test of the failure path (no counterpart in the reference): launches a matvec as the consumer of a two-rank
+ * exchange whose packets are never sent, with a probe limit of 64 instead of about a second. Every poll runs out, the
+ * kernel raises the error word and returns; the call then answers status 4 (what b200_decode and the other engine
+ * calls answer when a peer has gone away). No GPU fault is involved and the context stays usable. Status 1 means
+ * that the kernel failed to report the missing exchange. */
+int b200_selftest_exchange_timeout(void);
 /* Fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and shares the bytes). */
 int b200_nccl_unique_id(uint8_t* out128);
 /* The contiguous share [begin, end) of `units` that rank tp_rank of tp_size owns (used for the FFN blocks). */

@@ -22,6 +22,9 @@
 #include <vector>
 #include <algorithm>
 #include <exception>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #include "logger.h"
 #include "model.h"
@@ -43,6 +46,13 @@ extern "C" {
 const char* ref_last_error() { return g_err.c_str(); }
 
 void ref_logger_off() { Logger::set_level(Logger::Level::OFF); }
+
+// OpenMP threads of the reference's loops (a launcher may have set OMP_NUM_THREADS=1 for the whole process).
+void ref_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#endif
+}
 
 float ref_fp16_to_fp32(uint16_t h, int is_scale_field) {
   return fp16_to_fp32(h, is_scale_field != 0);

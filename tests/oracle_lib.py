@@ -89,6 +89,9 @@ def ref():
         L.ref_model_prefill.argtypes = [_vp, _vp, _i, _vp, _vp]
         L.ref_model_kv.argtypes = [_vp, _i, _i, _i, _vp]
         L.ref_logger_off()
+        if hasattr(L, "ref_set_threads"):
+            L.ref_set_threads.argtypes = [_i]
+            L.ref_set_threads.restype = None
         _ref = L
     return _ref
 

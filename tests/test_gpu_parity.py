@@ -450,6 +450,18 @@ def test_kv_reset_and_errors(pkg, tiny_models):
         pkg.Engine.from_gguf("/nonexistent/model.gguf")
 
 
+def test_bounded_wait_runs_out_and_is_reported(pkg, tiny_models):
+    """A consumer of a tensor-parallel exchange whose packets never arrive: the poll gives up after its (shortened)
+    limit, the kernel returns, status 4 comes back, and the same process keeps computing correctly afterwards."""
+    assert pkg.api.selftest_exchange_timeout() == 4
+    assert "bounded wait" in pkg.api.lib().b200_last_error().decode()
+    eng = pkg.Engine.from_gguf(tiny_models[1])
+    orc = ol.OracleModel.from_gguf(tiny_models[1])
+    lg, _ = eng.decode([5], [0])
+    assert np.abs(lg[0] - orc.decode(5, 0)).max() <= 2e-2
+    eng.close()
+
+
 def test_upload_tensor_path_and_validation(pkg, tiny_models):
     """create + upload_tensor + finalize gives the same engine as load_gguf; malformed input is refused."""
     g = pkg.gguf.GGUF(tiny_models[1])

@@ -32,7 +32,7 @@ EXPORTS = [
     "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
     "b200_fused_qkv_rope", "b200_fused_gate_up_swiglu", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
-    "b200_nccl_unique_id", "b200_tp_share"]
+    "b200_nccl_unique_id", "b200_tp_share", "b200_selftest_exchange_timeout"]
 
 _lib = None
 _vp, _i, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
@@ -297,6 +297,11 @@ def attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v
     """Allocation-free decode attention on caller-owned DEVICE buffers (integers = device addresses)."""
     _check(lib().b200_attention_decode_noalloc(d_q, d_kv_new, d_k_cache, d_v_cache, d_k_scale, d_v_scale, d_position, n_heads,
                                                n_kv_heads, head_dim, max_ctx, kv_dtype, n_splits, d_out, stream))
+
+
+def selftest_exchange_timeout():
+    """Returns the status of the failure-path self-test (4 = the bounded wait ran out and was reported)."""
+    return lib().b200_selftest_exchange_timeout()
 
 
 def nccl_unique_id():

@@ -535,6 +535,9 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
   auto slot_of = [&](void* region, int k, int src) {
     return static_cast<uint2*>(region) + ((size_t)(k & 1) * e->tp_size + src) * e->max_seqs * H;
   };
+  auto amax_of = [&](void* region) {  // argmax packets of the lm_head launch, behind the exchange slots: [rank][batch][parts]
+    return static_cast<uint2*>(region) + (size_t)2 * e->tp_size * e->max_seqs * H;
+  };
   float* hcur = e->d_h;
   float* hnext = e->d_h2;
   int pending = -1;  // exchange whose sum the next matvec has to pick up
@@ -639,10 +642,21 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
     p.amax_val = tp ? e->d_amax_val + half : e->d_amax_val; p.amax_idx = tp ? e->d_amax_idx + half : e->d_amax_idx;
     p.amax_row_offset = e->tp_rank * e->Vl;
+    // Peer mode: the step graph holds no collective call at all. Every rank's argmax partials travel as packets
+    // into every rank's exchange region (the matvec launch uses at most num_sms CTAs: parts_per_rank = its grid),
+    // and the logits shares stay local; calls that hand logits to the host gather them after the graph.
+    const int head_grid = std::max(1, std::min(e->out_w.tiles, e->num_sms));
+    const unsigned head_epoch_k = 2u * (unsigned)e->L + 1u;
+    if (peer) {
+      for (int r = 0; r < e->tp_size; ++r) p.amax_peer[r] = amax_of(e->peer_region[r]) + (size_t)e->tp_rank * batch * head_grid;
+      p.tp = e->tp_size; p.tp_rank = e->tp_rank;
+      p.epoch_base = e->d_epoch;
+      p.amax_epoch_k = head_epoch_k;
+    }
     p.trace = trace_rec(e, launches);
     int grid = 0;
     launches += launch_linear(e, p, batch, st, use_tc, &grid);
-    if (tp) {
+    if (tp && !peer) {
       Nccl& n = Nccl::get();
       n.check(n.AllGather(e->d_logits_local, e->d_logits, (size_t)batch * e->Vl, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
       n.check(n.AllGather(p.amax_val, e->d_amax_val, (size_t)batch * grid, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
@@ -654,7 +668,10 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid * e->tp_size; s.parts_per_rank = grid; s.batch = batch;
     s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
     s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
-    if (peer) { s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L; }  // the next step's packets carry new numbers
+    if (peer) {  // the next step's packets carry new numbers
+      s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L + 2u;
+      s.amax_pkts = amax_of(e->xregion); s.epoch_k = head_epoch_k; s.error_flag = e->d_error;
+    }
     select_kernel<<<1, 256, 0, st>>>(s);
     CK(cudaGetLastError());
     ++launches;

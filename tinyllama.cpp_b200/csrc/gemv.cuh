@@ -163,6 +163,9 @@ struct GemvParams {
   float* amax_val;      // optional per-CTA argmax partials [batch][gridDim.x]
   int* amax_idx;
   int amax_row_offset;  // added to the row index reported in amax_idx (vocabulary shard offset)
+  uint2* amax_peer[8];  // tensor parallel: where each rank receives this rank's argmax partials as packets
+                        // {value, index | (exchange number & 0x7fff) << 17}, [batch][gridDim.x] each; nullptr: not sent
+  unsigned amax_epoch_k; // number of that exchange within the step (added to *epoch_base)
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
@@ -184,6 +187,7 @@ struct GemvParams {
   const uint2* x_parts;         // [tp][parts_stride] local exchange slots (packets) to add to x
   size_t parts_stride;          // packets between the slots of consecutive ranks
   float* x_out;                 // [batch][x_stride] where CTA 0 stores the summed input
+  int poll_limit;               // probes of a packet before the consumer gives up (0: the default, about a second)
 };
 
 // ---- shared-memory activation image ------------------------------------------------------
@@ -851,6 +855,11 @@ __device__ __forceinline__ void gemv_store_argmax(const GemvParams& prm, GemvSha
       if (sh->sv[w] > bv || (sh->sv[w] == bv && sh->si[w] < bi)) { bv = sh->sv[w]; bi = sh->si[w]; }
     prm.amax_val[(size_t)bidx * ncta + cta] = bv;
     prm.amax_idx[(size_t)bidx * ncta + cta] = bi;
+    if (prm.amax_peer[0]) {
+      const unsigned tag = (*prm.epoch_base + prm.amax_epoch_k) & 0x7fffu;
+      const uint2 pkt = make_uint2(__float_as_uint(bv), ((unsigned)bi & 0x1ffffu) | (tag << 17));
+      for (int r = 0; r < prm.tp; ++r) prm.amax_peer[r][(size_t)bidx * ncta + cta] = pkt;
+    }
   }
 }
 
@@ -866,6 +875,7 @@ struct XLoad {
   size_t parts_stride;
   int nparts;
   unsigned tag;
+  int limit;           // probes before giving up
   float* out;          // nullptr: do not store
   int* fail;           // set when a poll gives up
   __device__ __forceinline__ void operator()(int e, float (&v)[8]) const {
@@ -884,7 +894,7 @@ struct XLoad {
           const bool ok = p[0].y == tag && p[0].w == tag && p[1].y == tag && p[1].w == tag && p[2].y == tag && p[2].w == tag && p[3].y == tag &&
                           p[3].w == tag;
           if (ok) break;
-          if (++it > (1 << 22)) {  // bounded (seconds): report instead of hanging when a rank has gone away
+          if (++it > limit) {  // bounded (about a second by default): report instead of hanging when a rank has gone away
             *reinterpret_cast<volatile int*>(fail) = 1;
             break;
           }
@@ -908,7 +918,7 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* 
   const int cta = blockIdx.x, ncta = gridDim.x, bidx = blockIdx.y;
   unsigned long long* rec = (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? prm.trace : nullptr;
   XLoad xfn{prm.x + (size_t)bidx * prm.x_stride, prm.x_parts ? prm.x_parts + (size_t)bidx * prm.x_stride : nullptr,
-            prm.parts_stride, prm.tp, prm.x_parts ? *prm.epoch_base + prm.epoch_k : 0u,
+            prm.parts_stride, prm.tp, prm.x_parts ? *prm.epoch_base + prm.epoch_k : 0u, prm.poll_limit > 0 ? prm.poll_limit : (1 << 22),
             (prm.x_out && cta == 0) ? prm.x_out + (size_t)bidx * prm.x_stride : nullptr, &sh->xfail};
   auto after_x = [&](float ss) {
     uint32_t z;
@@ -925,7 +935,9 @@ __device__ __forceinline__ void gemv_consume(const GemvParams& prm, GemvShared* 
     trace_stamp(rec, 3);
   };
   act_build<P>(smem, xfn, prm.norm_w, prm.eps, prm.K, sh->red, before_x, after_x);
-  if (prm.x_parts && threadIdx.x == 0 && *(volatile int*)&sh->xfail) pipe_fail(prm, sh);  // act_build ended with a barrier: every poll is over
+  // act_build ended with a barrier: every poll is over. A poll that gave up is reported through the error word; the
+  // weight pipeline itself is intact, so the launch runs to its end (on a meaningless input vector) and returns.
+  if (prm.x_parts && threadIdx.x == 0 && *(volatile int*)&sh->xfail && prm.error_flag) *reinterpret_cast<volatile int*>(prm.error_flag) = 1;
   trace_stamp(rec, 5);
   const ActImage a = act_carve(smem, prm.K, P);
 

@@ -35,12 +35,18 @@ struct SelectParams {
   int log_cap;
   unsigned* epoch;        // tensor-parallel exchange counter to advance at the end of the step, or nullptr
   unsigned epoch_inc;
+  // tensor parallel over peer memory: the partials arrive as packets {value, index | (number & 0x7fff) << 17} in
+  // amax_pkts (same [ranks][batch][parts_per_rank] order) and are polled (bounded) instead of read from amax_val / amax_idx
+  const uint2* amax_pkts;
+  unsigned epoch_k;       // this exchange's number = *epoch + epoch_k
+  int* error_flag;
 };
 
 __global__ void select_kernel(const SelectParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int step = *p.step_counter;
   const int fsteps = p.forced ? *p.forced_steps : 0;
+  const unsigned want = p.amax_pkts ? ((*p.epoch + p.epoch_k) & 0x7fffu) : 0u;
 #pragma unroll 1
   for (int b = warp; b < p.batch; b += nwarps) {
     float bv = -INFINITY;
@@ -48,8 +54,26 @@ __global__ void select_kernel(const SelectParams p) {
 #pragma unroll 1
     for (int i = lane; i < p.nparts; i += 32) {
       const size_t at = ((size_t)(i / p.parts_per_rank) * p.batch + b) * p.parts_per_rank + (i % p.parts_per_rank);
-      const float v = p.amax_val[at];
-      const int idx = p.amax_idx[at];
+      float v;
+      int idx;
+      if (p.amax_pkts) {
+        uint2 pk;
+        int it = 0;
+        while (true) {
+          asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(pk.x), "=r"(pk.y) : "l"(p.amax_pkts + at));
+          if ((pk.y >> 17) == want) break;
+          if (++it > (1 << 22)) {  // bounded: a rank has gone away
+            if (p.error_flag) *reinterpret_cast<volatile int*>(p.error_flag) = 1;
+            break;
+          }
+          if (it > 16) __nanosleep(32);
+        }
+        v = __uint_as_float(pk.x);
+        idx = (int)(pk.y & 0x1ffffu);
+      } else {
+        v = p.amax_val[at];
+        idx = p.amax_idx[at];
+      }
       if (v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
     }
 #pragma unroll

@@ -13,6 +13,9 @@
 #include <cstring>
 #include <string>
 #include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 namespace {
 
@@ -224,6 +227,15 @@ void kv_str(std::vector<uint8_t>& v, const char* k, const char* s) { put_str(v, 
 }  // namespace
 
 extern "C" {
+
+// Worker threads of the generator / quantizers (a launcher may have set OMP_NUM_THREADS=1 for the whole process).
+void b200_synth_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 
 struct b200_synth_config {
   int32_t hidden, ffn, n_heads, n_kv_heads, n_layers, vocab, max_pos;

@@ -40,6 +40,13 @@ def lib():
         _lib.b200_synth_quantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
         _lib.b200_synth_fill_normal.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float]
         _lib.b200_synth_fill_normal.restype = None
+        _lib.b200_synth_set_threads.argtypes = [ctypes.c_int]
+        _lib.b200_synth_set_threads.restype = None
+        # a launcher (torchrun) may have pinned OMP_NUM_THREADS to 1 for the process: the writer uses the cores it may run on
+        try:
+            _lib.b200_synth_set_threads(len(os.sched_getaffinity(0)))
+        except AttributeError:
+            _lib.b200_synth_set_threads(os.cpu_count() or 1)
     return _lib
 
 
