@@ -152,8 +152,8 @@ int b200_attention_prefill(const float* q, const float* k_rows, const float* v_r
                            int n_heads, int n_kv_heads, int head_dim, int kv_dtype, float* out);
 
 /* No counterpart in the reference. Decode attention for callers that must not allocate device
- * memory at the moment of the call (stream capture in progress, memory handed out once by an
- * external pool, allocator frozen after start-up). All pointers are DEVICE pointers owned by the
+ * memory at the moment of the call (memory handed out once at start-up by an external pool the library
+ * does not know, allocator frozen after initialisation, a latency budget that excludes cudaMalloc). All pointers are DEVICE pointers owned by the
  * caller: q [n_heads][hd]; kv_new = new K rows then new V rows [2][n_kv][hd] (already rotated);
  * k_cache / v_cache [n_kv][max_ctx][hd] (FP32, or int8 with k_scale / v_scale [n_kv][max_ctx]);
  * position = one int, the index of the new token (rows 0..position-1 of the caches are read, row

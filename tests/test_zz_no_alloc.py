@@ -1,8 +1,8 @@
 """The allocation-free attention entry point against the ordinary one.
 
 b200_attention_decode_noalloc is for callers that cannot allocate device memory when they call
-(a stream capture is open, memory comes from a pool sized once at start-up, the allocator is
-frozen): they pass device buffers they already own and the library uses its built-in scratch.
+(memory comes from a pool sized once at start-up, the allocator is frozen after initialisation,
+there is no room for cudaMalloc in the latency budget): they pass device buffers they already own and the library uses its built-in scratch.
 This file sorts last on purpose, so that a run that stops at the first failure has already been
 through every other test. It holds device memory through torch only because the test needs some
 owner for the buffers; the entry point itself never sees torch.
