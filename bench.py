@@ -267,9 +267,10 @@ def main():
     vocab = eng.vocab
     pr = prompts(batch, prompt_len, vocab)
     t_prefill = time.perf_counter()
-    first = []
-    for s in range(batch):
-        first.append(int(eng.prefill(pr[s], slot=s).argmax()))
+    if batch > 1:  # all prompts in one sequence-aware call (shared 512-token chunks)
+        first = [int(v.argmax()) for v in eng.prefill_batch(pr)]
+    else:
+        first = [int(eng.prefill(pr[0], slot=0).argmax())]
     t_prefill = time.perf_counter() - t_prefill
     if rank == 0:
         progress(f"prompts ingested in {t_prefill:.1f} s")

@@ -86,6 +86,17 @@ int b200_forward(b200_engine* e, int seq_slot, float* host_x, int pos, float* ho
 int b200_prefill(b200_engine* e, int seq_slot, const int32_t* token_ids, int n, int start_pos,
                  float* host_logits_last /* [vocab] */);
 
+/* Sequence-aware prompt ingestion of several sequences in one call (the batch prefill of
+ * TinyLlamaSession::generate_batch, api.cpp:1144-1421, with attention_batch_cpu_sequence_aware,
+ * cpu_attention.cpp:203-325): the prompts are laid end to end (token_ids holds lens[0] + lens[1] + ... ids) and cut
+ * into chunks of 512 tokens, so that short prompts share a chunk and its weight traffic; every token carries its own
+ * position and KV slot, and each token attends only to its own sequence's rows. Always the tensor-core path.
+ * Sequence s occupies positions start_pos[s] .. start_pos[s]+lens[s]-1 of slot slots[s] (slots distinct).
+ * host_logits_last [n_seqs][vocab] (logits after each prompt's last token) may be NULL. Same kernels and the same
+ * per-token arithmetic as one b200_prefill call per sequence on the tensor-core path (n >= 16). */
+int b200_prefill_batch(b200_engine* e, int n_seqs, const int32_t* slots, const int32_t* token_ids, const int32_t* lens,
+                       const int32_t* start_pos, float* host_logits_last);
+
 /* One decode step for `batch` independent sequences: forward_device_batch_generation
  * (model.cpp:1863) with the embedding lookup of the session loop (api.cpp:727) folded in.
  * host_logits [batch][vocab] and argmax_out [batch] are each optional (NULL). argmax follows

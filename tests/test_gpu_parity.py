@@ -397,6 +397,44 @@ def test_batch_decode_grouped_query_attention_long_contexts(pkg, tiny_models, kv
     eng.close()
 
 
+@pytest.mark.parametrize("kv", ["f32", "i8"])
+def test_prefill_batch_equals_one_call_per_sequence(pkg, tiny_models, kv):
+    """Sequence-aware ingestion of ragged prompts in shared 512-token chunks (nine sequences, 860 tokens: two chunks, a
+    prompt that straddles the chunk border, prompts shorter than a tile) against one b200_prefill call per sequence:
+    logits and the following decode step agree to 1e-4 (each token's matmul column and attention rows are its own, so
+    the two differ at most by the order of a few fp32 additions where a prompt straddles a chunk border); and against
+    the oracle with the tensor-core path's tolerance."""
+    kvd = pkg.KV_I8 if kv == "i8" else pkg.KV_F32
+    lens = [120, 17, 100, 127, 64, 99, 111, 125, 97]
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(0, 512, n).astype(np.int32) for n in lens]
+    slots = [3, 0, 8, 1, 7, 2, 6, 4, 5]
+    a = pkg.Engine.from_gguf(tiny_models[1], max_seqs=9, kv_dtype=kvd)
+    b = pkg.Engine.from_gguf(tiny_models[1], max_seqs=9, kv_dtype=kvd)
+    got = a.prefill_batch(prompts, slots=slots)
+    exact = 0
+    for i, p in enumerate(prompts):
+        one = b.prefill(p, slot=slots[i])
+        assert np.abs(got[i] - one).max() <= 1e-4, i
+        exact += int(np.array_equal(got[i], one))
+    print(f"prefill_batch: {exact} of {len(prompts)} prompts bit-identical to the per-sequence call")
+    toks = [int(g.argmax()) for g in got]
+    la, _ = a.decode(toks[:4], lens[:4], slots=slots[:4])
+    lb, _ = b.decode(toks[:4], lens[:4], slots=slots[:4])
+    assert np.abs(la - lb).max() <= 1e-4
+    orc = ol.OracleModel.from_gguf(tiny_models[1], kv_int8=(kv == "i8"), max_seqs=9)
+    for i in (1, 3):
+        ref = orc.prefill(prompts[i], seq=slots[i])
+        tol = 2e-2 if kv == "f32" else max(2e-2, 1.5e-2 * float(np.abs(ref).max()))
+        assert np.abs(got[i] - ref).max() <= tol
+    with pytest.raises(pkg.B200Error, match="same KV slot"):
+        a.prefill_batch(prompts[:2], slots=[1, 1])
+    with pytest.raises(pkg.B200Error, match="exceeds the KV capacity"):
+        a.prefill_batch([np.zeros(200, np.int32)], slots=[0])
+    a.close()
+    b.close()
+
+
 def test_forward_from_hidden_state(pkg, tiny_models):
     """b200_forward mirrors TinyLlamaModel::forward: hidden vector in, logits out, input updated in place."""
     eng = pkg.Engine.from_gguf(tiny_models[1])

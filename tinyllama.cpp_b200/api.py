@@ -28,7 +28,7 @@ class ModelDesc(ctypes.Structure):
 EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
-    "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_decode",
+    "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_prefill_batch", "b200_decode",
     "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
     "b200_fused_qkv_rope", "b200_fused_gate_up_swiglu", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
@@ -60,6 +60,7 @@ def lib():
     L.b200_forward.argtypes = [_vp, _i, _vp, _i, _vp]
     L.b200_prefill.argtypes = [_vp, _i, _vp, _i, _i, _vp]
     L.b200_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
+    L.b200_prefill_batch.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
     L.b200_generate_greedy.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, ctypes.POINTER(ctypes.c_float)]
     L.b200_dequant.argtypes = [_i, _vp, _sz, _vp]
     L.b200_matvec.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _i, _vp]
@@ -171,6 +172,17 @@ class Engine:
         ids = _i32(ids)
         logits = np.empty(self.vocab, np.float32) if want_logits else None
         _check(lib().b200_prefill(self._h, slot, _ptr(ids), len(ids), start_pos, _ptr(logits)))
+        return logits
+
+    def prefill_batch(self, prompts, slots=None, start_pos=None, want_logits=True):
+        """Ingests several prompts in one call (sequence-aware chunks of 512 tokens); returns logits [n][vocab] or None."""
+        n = len(prompts)
+        lens = _i32([len(p) for p in prompts])
+        ids = _i32(np.concatenate([np.asarray(p, np.int32) for p in prompts]))
+        slots = _i32(slots if slots is not None else np.arange(n))
+        start = _i32(start_pos if start_pos is not None else np.zeros(n))
+        logits = np.empty((n, self.vocab), np.float32) if want_logits else None
+        _check(lib().b200_prefill_batch(self._h, n, _ptr(slots), _ptr(ids), _ptr(lens), _ptr(start), _ptr(logits)))
         return logits
 
     def decode(self, tokens, positions, slots=None, want_logits=True, want_argmax=True):

@@ -709,17 +709,25 @@ static void ensure_prefill_buffers(b200_engine* e) {
   e->pf_cap = T;
 }
 
-// One chunk of T <= PF_CHUNK prompt tokens of sequence `slot` at positions start .. start+T-1.
-// last: also leave the logits of the chunk's last token in e->d_logits.
-static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, int start, bool last) {
+// A run of consecutive tokens of one sequence inside a chunk: rows [row0, row0 + len) of the chunk's buffers hold the
+// tokens at positions start .. start+len-1 of KV slot `slot`. logits_to >= 0: this run ends its sequence's prompt,
+// and the logits of its last token go to row logits_to of the caller's host buffer.
+struct PrefillRun {
+  int row0, len, slot, start, logits_to;
+};
+
+// One chunk of T <= PF_CHUNK prompt tokens, possibly of several sequences (sequence-aware: every token carries its
+// own position and KV slot through the RoPE epilogue and the cache append, and attention runs per run of tokens,
+// each over its own sequence's cache rows; reference api.cpp:1144-1421 / cpu_attention.cpp:203-325).
+// meta = token ids | positions | slots, T each. After the layers, the logits of the last token of every run with
+// logits_to >= 0 are computed and copied to host_logits + logits_to * V (nullptr: left in e->d_logits only).
+static void prefill_chunk(b200_engine* e, int T, const std::vector<int>& meta, const std::vector<PrefillRun>& runs, float* host_logits) {
   ensure_prefill_buffers(e);
   cudaStream_t st = e->stream;
   const int H = e->H, F = e->F, KVD = e->KVD;
   const bool tp = e->tp_size > 1;
-  std::vector<int> meta((size_t)3 * T);
-  for (int t = 0; t < T; ++t) { meta[t] = ids[t]; meta[T + t] = start + t; meta[2 * T + t] = slot; }
   CK(cudaMemcpyAsync(e->pf_ints, meta.data(), meta.size() * 4, cudaMemcpyHostToDevice, st));
-  CK(cudaStreamSynchronize(st));  // meta is a stack-lifetime buffer
+  CK(cudaStreamSynchronize(st));  // meta may not outlive this call
   const int* d_tok = e->pf_ints;
   const int* d_pos = e->pf_ints + T;
   const int* d_slot = e->pf_ints + 2 * T;
@@ -742,12 +750,14 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
                                                         w.v_cache, w.k_scale, w.v_scale);
     CK(cudaGetLastError());
     if (prefill_attn_available(e->hd)) {
-      PrefillAttnParams a{};
-      a.q = e->pf_q; a.q_stride = e->Hq;
-      a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
-      a.slot = slot; a.start = start; a.T = T; a.nq = e->nq; a.nkv = e->nkv; a.max_ctx = e->max_ctx;
-      a.out = e->pf_attn; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
-      launch_prefill_attention(a, i8, e->hd, st);
+      for (const PrefillRun& r : runs) {
+        PrefillAttnParams a{};
+        a.q = e->pf_q + (size_t)r.row0 * e->Hq; a.q_stride = e->Hq;
+        a.k_cache = w.k_cache; a.v_cache = w.v_cache; a.k_scale = w.k_scale; a.v_scale = w.v_scale;
+        a.slot = r.slot; a.start = r.start; a.T = r.len; a.nq = e->nq; a.nkv = e->nkv; a.max_ctx = e->max_ctx;
+        a.out = e->pf_attn + (size_t)r.row0 * e->Hq; a.out_stride = e->Hq; a.att_scale = 1.0f / std::sqrt((float)e->hd);
+        launch_prefill_attention(a, i8, e->hd, st);
+      }
     } else {
       AttnParams a{};
       a.q = e->pf_q; a.kv_new = e->pf_kvnew; a.q_stride = e->Hq; a.kvn_stride = 2 * KVD;
@@ -781,17 +791,52 @@ static void prefill_chunk(b200_engine* e, int slot, const int32_t* ids, int T, i
       if (tp) tp_reduce_add(e, T, st, e->pf_h, e->pf_partial);
     }
   }
-  if (last) {  // final norm + lm_head for the last token only, on the matvec kernel
+  for (const PrefillRun& r : runs) {  // final norm + lm_head for the last token of a prompt only, on the matvec kernel
+    if (r.logits_to < 0) continue;
     GemvParams p{};
-    p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->pf_h + (size_t)(T - 1) * H; p.x_stride = H;
+    p.seg[0] = seg_of(e->out_w); p.nseg = 1; p.K = H; p.x = e->pf_h + (size_t)(r.row0 + r.len - 1) * H; p.x_stride = H;
     p.norm_w = e->out_norm.f32(); p.eps = eps; p.epi = EPI_STORE; p.y = tp ? e->d_logits_local : e->d_logits; p.y_stride = e->Vl;
     launch_gemv(e, p, 1, st);
     if (tp) {  // every rank holds its share of the vocabulary: gather the shares (in rank order = vocabulary order for one row)
       Nccl& n = Nccl::get();
       n.check(n.AllGather(e->d_logits_local, e->d_logits, (size_t)e->Vl, Nccl::kFloat32, e->nccl_comm, st), "ncclAllGather");
     }
+    if (host_logits) CK(cudaMemcpyAsync(host_logits + (size_t)r.logits_to * e->V, e->d_logits, (size_t)e->V * 4, cudaMemcpyDeviceToHost, st));
   }
 }
+
+// Prompt ingestion of one or several sequences through the tensor-core path: the tokens of all sequences are laid
+// end to end and cut into chunks of PF_CHUNK, so that short prompts share a chunk (and its weight traffic).
+// host_logits: [n_seqs][V] or nullptr.
+static void prefill_sequences(b200_engine* e, int n_seqs, const int32_t* slots, const int32_t* ids, const int32_t* lens, const int32_t* start_pos,
+                              float* host_logits) {
+  std::vector<int> meta;
+  std::vector<PrefillRun> runs;
+  auto flush = [&](int T) {
+    // meta holds [id, pos, slot] triples of T tokens: regroup into the three arrays the kernels read
+    std::vector<int> m((size_t)3 * T);
+    for (int t = 0; t < T; ++t) { m[t] = meta[3 * t]; m[T + t] = meta[3 * t + 1]; m[2 * T + t] = meta[3 * t + 2]; }
+    prefill_chunk(e, T, m, runs, host_logits);
+    meta.clear();
+    runs.clear();
+  };
+  int T = 0;
+  size_t off = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    int done = 0;
+    while (done < lens[s]) {
+      const int take = std::min(lens[s] - done, PF_CHUNK - T);
+      runs.push_back({T, take, slots[s], start_pos[s] + done, done + take == lens[s] ? s : -1});
+      for (int t = 0; t < take; ++t) { meta.push_back(ids[off + done + t]); meta.push_back(start_pos[s] + done + t); meta.push_back(slots[s]); }
+      T += take;
+      done += take;
+      if (T == PF_CHUNK) { flush(T); T = 0; }
+    }
+    off += (size_t)lens[s];
+  }
+  if (T > 0) flush(T);
+}
+
 
 static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {
   const int key = batch * 2 + (with_embed ? 1 : 0);
