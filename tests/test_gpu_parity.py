@@ -415,13 +415,13 @@ def test_prefill_batch_equals_one_call_per_sequence(pkg, tiny_models, kv):
     exact = 0
     for i, p in enumerate(prompts):
         one = b.prefill(p, slot=slots[i])
-        assert np.abs(got[i] - one).max() <= 1e-4, i
+        assert np.abs(got[i] - one).max() <= (1e-4 if kv == "f32" else max(1e-4, 1.5e-2 * float(np.abs(one).max()))), i
         exact += int(np.array_equal(got[i], one))
     print(f"prefill_batch: {exact} of {len(prompts)} prompts bit-identical to the per-sequence call")
     toks = [int(g.argmax()) for g in got]
     la, _ = a.decode(toks[:4], lens[:4], slots=slots[:4])
     lb, _ = b.decode(toks[:4], lens[:4], slots=slots[:4])
-    assert np.abs(la - lb).max() <= 1e-4
+    assert np.abs(la - lb).max() <= (1e-4 if kv == "f32" else max(1e-4, 1.5e-2 * float(np.abs(lb).max())))
     orc = ol.OracleModel.from_gguf(tiny_models[1], kv_int8=(kv == "i8"), max_seqs=9)
     for i in (1, 3):
         ref = orc.prefill(prompts[i], seq=slots[i])
