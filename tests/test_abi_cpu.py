@@ -55,6 +55,30 @@ def test_create_rejects_head_sizes_the_kernels_do_not_map(pkg):
             pkg.Engine.create(bad)
 
 
+def test_header_compiles_as_c_and_cpp(tmp_path):
+    """The boundary header is plain C: it must go through a C11 and a C++17 compiler on its own."""
+    import subprocess
+    inc = os.path.join(ROOT, "include")
+    (tmp_path / "c.c").write_text('#include "b200llama.h"\nint main(void) { return B200_KV_I8 == 1 ? 0 : 1; }\n')
+    (tmp_path / "cpp.cpp").write_text('#include "b200llama.h"\nint main() { b200_model_desc d{}; return d.tp_size; }\n')
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(tmp_path / "c.c")], check=True)
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(tmp_path / "cpp.cpp")], check=True)
+
+
+def test_reference_side_adapter_compiles_and_links(pkg, tmp_path):
+    """The adapter of INTEGRATION.md (TinyLlamaModel / KVCache members forwarded to the C ABI) compiles with g++,
+    links against libb200llama.so alone and, run without a model file, reports the library's error instead of crashing."""
+    import subprocess
+    pkg.api.lib()
+    so_dir = os.path.join(ROOT, "tinyllama.cpp_b200", "csrc")
+    exe = str(tmp_path / "adapter_check")
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "abi", "adapter_check.cpp"),
+                    "-o", exe, "-L", so_dir, "-lb200llama", f"-Wl,-rpath,{so_dir}"], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert "init failed as expected" in r.stdout, (r.stdout, r.stderr)
+    assert r.returncode in (0, 1)  # 0 without a GPU, 1 with one (the model file does not exist either way)
+
+
 def test_product_never_touches_oracle():
     """Nothing under the package or the C ABI may reference the oracle folder."""
     for root, _, files in os.walk(os.path.join(ROOT, "tinyllama.cpp_b200")):

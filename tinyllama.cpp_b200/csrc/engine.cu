@@ -279,7 +279,9 @@ static int launch_gemv(const b200_engine* e, GemvParams p, int batch, cudaStream
   // ring depth: what fits, but no more slots than this CTA will ever fill
   const int stages_per_cta = ((p.ntiles + gx - 1) / gx) * p.nslab;
   const int nstages = std::max(1, (int)std::min<size_t>(std::min(GEMV_MAX_STAGES, stages_per_cta), (budget - ring_off) / p.slot_bytes));
-  p.early_stages = std::max(1, std::min(nstages, (int)(80 * 1024 / p.slot_bytes)));
+  // bytes the producer requests before the consumers hold their input vector (B200_GEMV_EARLY_KB, default 80)
+  static const int early_kb = [] { const char* v = getenv("B200_GEMV_EARLY_KB"); return v && atoi(v) > 0 ? atoi(v) : 80; }();
+  p.early_stages = std::max(1, std::min(nstages, (int)((size_t)early_kb * 1024 / p.slot_bytes)));
   p.error_flag = e->d_error;
   const size_t smem = ring_off + (size_t)nstages * p.slot_bytes;
   cudaLaunchConfig_t cfg{};
