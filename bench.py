@@ -56,7 +56,7 @@ def peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clocks and throttle reasons while the run lasts (read-only): through NVML every 20 ms when the
+    """Samples SM clocks and throttle reasons while the run lasts (read-only): through NVML every 5 ms when the
     Python binding is there, else through nvidia-smi every 200 ms."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -100,7 +100,7 @@ class ClockSampler(threading.Thread):
                     self._sample_smi()
             except Exception:
                 pass
-            self._stop_evt.wait(0.02 if self.nvml else 0.2)
+            self._stop_evt.wait(0.005 if self.nvml else 0.2)
 
     def finish(self):
         self._stop_evt.set()
