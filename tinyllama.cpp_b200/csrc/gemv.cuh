@@ -16,17 +16,18 @@
 // Data movement. Weights live in HBM as "stage images": the matrix is cut into tiles of 16*R
 // rows and slabs of S <= 16 blocks along K, and each (tile, slab) is stored as one contiguous
 // run laid out exactly as it will sit in shared memory (rows padded to a stride = 32 mod 128 so
-// the fragment loads are free of bank conflicts). One persistent CTA per SM walks its tiles;
-// every stage moves with ONE bulk asynchronous copy (cp.async.bulk, completion counted on an
-// mbarrier) into a ring of shared-memory slots, so HBM sees runs of 20-70 KB and several stages
-// are in flight without holding registers. There is no producer warp: the warp that is last to
-// finish with a slot requests the stage that goes into it next, so all 512 threads compute and
-// each may use 128 registers. The 16 warps each take one (row group, block) task of the staged slab. When a row has at most 16 blocks a
+// the fragment loads are free of bank conflicts). One persistent CTA per SM walks its tiles:
+// 16 consumer warps and one producer warp. One lane of the producer requests every stage with ONE
+// bulk asynchronous copy (cp.async.bulk, completion counted on an mbarrier) into a ring of
+// shared-memory slots as soon as the slot is empty (a second mbarrier per slot counts the consumer
+// warps that are done with it), so HBM sees runs of 20-70 KB, several stages are in flight
+// without holding registers, and the consumers contain no copy code at all. The 16 consumer warps
+// each take one (row group, block) task of the staged slab. When a row has at most 16 blocks a
 // warp meets the same block column in every tile, and its B fragments (the activation digits)
 // stay in registers for the whole launch. Partial row sums are parked in shared memory and the
 // rows of up to 16 tiles are finished together, in a fixed order (deterministic), by all threads.
-// The kernel supports programmatic dependent launch: weights are prefetched while the previous
-// kernel drains, and only then does it wait for that kernel's results.
+// The kernel supports programmatic dependent launch: the producer never depends on the previous
+// kernel and starts at once; only the consumers wait for that kernel's results.
 //
 // HBM traffic per launch = the packed bytes of the rows (each read exactly once, plus the row
 // padding: 1.4 % for a 4096-wide Q4_K matrix) plus the activation vector.
