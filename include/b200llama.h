@@ -113,6 +113,17 @@ int b200_generate_greedy(b200_engine* e, int batch, const int32_t* first_tokens,
                          const int32_t* start_positions, const int32_t* seq_slots, int steps,
                          int32_t* out_tokens, float* elapsed_ms);
 
+/* The same loop with the reference's repetition penalty applied on the device before every argmax
+ * (apply_repetition_penalty, api.cpp:86-97, called from TinyLlamaSession::generate, api.cpp:678, 768; default 1.3):
+ * every occurrence of a token id among the last 64 GENERATED ids turns its logit l into l / penalty when l > 0 and
+ * l * penalty otherwise (an id that occurs twice is penalised twice); each chosen id then joins that window.
+ * history holds the ids each sequence has generated so far, end to end (history_lens[b] of them for sequence b;
+ * normally just first_tokens[b], the id sampled after the prompt, which the reference has already pushed);
+ * both may be NULL for an empty history. Batches below the tensor-core switch point (16) only. */
+int b200_generate_greedy_penalized(b200_engine* e, int batch, const int32_t* first_tokens, const int32_t* start_positions,
+                                   const int32_t* seq_slots, int steps, float repetition_penalty, const int32_t* history,
+                                   const int32_t* history_lens, int32_t* out_tokens, float* elapsed_ms);
+
 /* ---- op level, for parity tests (cuda_kernels.h op layer) ---- */
 /* Exact dequantizers: dequantize_q8_0_block / dequantize_q4_k_m / dequantize_q6_k
  * (quantization.cpp:1047-1052, 171-221, 223-266); bit-exact, no fused multiply-add. */

@@ -311,6 +311,39 @@ def test_generate_greedy_matches_stepwise_and_oracle(pkg, tiny_models):
     eng.close()
 
 
+def _penalise(logits, generated, penalty, window=64):
+    """apply_repetition_penalty of the reference (api.cpp:86-97), restated: once per occurrence in the window."""
+    out = logits.copy()
+    for tid in generated[-window:]:
+        out[tid] = np.float32(out[tid] / np.float32(penalty)) if out[tid] > 0 else np.float32(out[tid] * np.float32(penalty))
+    return out
+
+
+@pytest.mark.parametrize("penalty", [1.3, 1.0])
+def test_generate_greedy_with_repetition_penalty_on_device(pkg, tiny_models, penalty):
+    """The device-resident loop with the reference's repetition penalty (default 1.3 in TinyLlamaSession::generate)
+    against the oracle's logits put through a restatement of apply_repetition_penalty + first-maximum argmax: 100
+    steps, so ids leave the 64-token window again, for two sequences with different histories."""
+    eng = pkg.Engine.from_gguf(tiny_models[1], max_seqs=2)
+    orc = ol.OracleModel.from_gguf(tiny_models[1], max_seqs=2)
+    firsts, hist = [5, 400], [[9, 5], [400]]
+    out, _ = eng.generate_greedy_penalized(firsts, [0, 0], 100, penalty, histories=hist)
+    for b in range(2):
+        gen, tok = list(hist[b]), firsts[b]
+        exact = 0
+        for pos in range(100):
+            lg = _penalise(orc.decode(tok, pos, seq=b), gen, penalty)
+            tok = int(out[pos, b])  # follow the engine's choice, so that one near-tie cannot derail the rest of the check
+            exact += int(tok == int(lg.argmax()))
+            assert lg[tok] >= lg.max() - 1e-3, (b, pos, tok, int(lg.argmax()))
+            gen.append(tok)
+        assert exact >= 98, exact
+    if penalty > 1.0:  # the penalty changes the sequence (a tiny model falls into a cycle without it)
+        plain, _ = pkg.Engine.from_gguf(tiny_models[1], max_seqs=2).generate_greedy(firsts, [0, 0], 100)
+        assert not np.array_equal(plain, out)
+    eng.close()
+
+
 def test_batch_decode_ragged_positions_and_slots(pkg, tiny_models):
     """Independent sequences at different positions, mapped to shuffled KV slots."""
     eng = pkg.Engine.from_gguf(tiny_models[3], max_seqs=4)

@@ -29,7 +29,7 @@ EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
     "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_prefill_batch", "b200_decode",
-    "b200_generate_greedy", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
+    "b200_generate_greedy", "b200_generate_greedy_penalized", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
     "b200_fused_qkv_rope", "b200_fused_gate_up_swiglu", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
     "b200_nccl_unique_id", "b200_tp_share", "b200_selftest_exchange_timeout"]
@@ -62,6 +62,7 @@ def lib():
     L.b200_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
     L.b200_prefill_batch.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
     L.b200_generate_greedy.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, ctypes.POINTER(ctypes.c_float)]
+    L.b200_generate_greedy_penalized.argtypes = [_vp, _i, _vp, _vp, _vp, _i, ctypes.c_float, _vp, _vp, _vp, ctypes.POINTER(ctypes.c_float)]
     L.b200_dequant.argtypes = [_i, _vp, _sz, _vp]
     L.b200_matvec.argtypes = [_i, _vp, _i64, _i64, _vp, _i, _i, _vp]
     L.b200_rmsnorm.argtypes = [_vp, _vp, _i, ctypes.c_float, _vp]
@@ -202,6 +203,21 @@ class Engine:
         ms = ctypes.c_float(0)
         _check(lib().b200_generate_greedy(self._h, b, _ptr(first_tokens), _ptr(start_positions), _ptr(slots), steps,
                                           _ptr(out), ctypes.byref(ms)))
+        return out, ms.value
+
+    def generate_greedy_penalized(self, first_tokens, start_positions, steps, penalty, histories=None, slots=None):
+        """Greedy loop with the reference's repetition penalty on the device; histories: per sequence, the ids generated so far."""
+        first_tokens, start_positions = _i32(np.atleast_1d(first_tokens)), _i32(np.atleast_1d(start_positions))
+        b = len(first_tokens)
+        slots = _i32(slots) if slots is not None else None
+        hist = lens = None
+        if histories is not None:
+            lens = _i32([len(h) for h in histories])
+            hist = _i32(np.concatenate([np.asarray(h, np.int32) for h in histories])) if int(lens.sum()) else _i32(np.zeros(1))
+        out = np.empty((steps, b), np.int32)
+        ms = ctypes.c_float(0)
+        _check(lib().b200_generate_greedy_penalized(self._h, b, _ptr(first_tokens), _ptr(start_positions), _ptr(slots), steps, penalty,
+                                                    _ptr(hist), _ptr(lens), _ptr(out), ctypes.byref(ms)))
         return out, ms.value
 
     def stats(self):

@@ -522,7 +522,7 @@ static int launch_linear(b200_engine* e, GemvParams p, int batch, cudaStream_t s
 // Per layer: [RMSNorm + QKV + RoPE] -> [KV append + attention] -> [O proj + residual] ->
 // [RMSNorm + gate/up + SwiGLU] -> [down proj + residual]; then [RMSNorm + lm_head + argmax
 // partials] and token selection. Returns the number of kernel launches.
-static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, bool with_embed, int* head_ctas_out) {
+static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, bool with_embed, int* head_ctas_out, bool penalized = false) {
   int launches = 0;
   const int H = e->H, F = e->F, KVD = e->KVD;
   const float eps = std::max(e->desc.rms_norm_eps, 1e-5f);  // reference utils.cpp:666-667
@@ -647,6 +647,10 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     // Peer mode: the step graph holds no collective call at all. Every rank's argmax partials travel as packets
     // into every rank's exchange region (the matvec launch uses at most num_sms CTAs: parts_per_rank = its grid),
     // and the logits shares stay local; calls that hand logits to the host gather them after the graph.
+    if (penalized) {
+      if (use_tc) throw std::runtime_error("the repetition penalty of the device loop is built for the matvec path (batch < " + std::to_string(e->gemm_min_batch) + ")");
+      p.pen_counts = e->d_pen_counts; p.pen_stride = e->pen_stride; p.pen_value = e->d_pen_value;
+    }
     const int head_grid = std::max(1, std::min(e->out_w.tiles, e->num_sms));
     const unsigned head_epoch_k = 2u * (unsigned)e->L + 1u;
     if (peer) {
@@ -670,6 +674,7 @@ static int enqueue_step(b200_engine* e, int batch, int nsplit, cudaStream_t st, 
     s.amax_val = e->d_amax_val; s.amax_idx = e->d_amax_idx; s.nparts = grid * e->tp_size; s.parts_per_rank = grid; s.batch = batch;
     s.tokens = e->d_tokens; s.positions = e->d_positions; s.argmax_out = e->d_argmax; s.step_counter = e->d_step;
     s.forced = e->d_forced; s.forced_steps = e->d_forced_steps; s.log = e->d_log; s.log_cap = e->log_cap;
+    if (penalized) { s.pen_ring = e->d_pen_ring; s.pen_count = e->d_pen_count; s.pen_counts = e->d_pen_counts; s.pen_stride = e->pen_stride; }
     if (peer) {  // the next step's packets carry new numbers
       s.epoch = e->d_epoch; s.epoch_inc = 2u * (unsigned)e->L + 2u;
       s.amax_pkts = amax_of(e->xregion); s.epoch_k = head_epoch_k; s.error_flag = e->d_error;
@@ -840,8 +845,8 @@ static void prefill_sequences(b200_engine* e, int n_seqs, const int32_t* slots, 
 }
 
 
-static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {
-  const int key = batch * 2 + (with_embed ? 1 : 0);
+static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true, bool penalized = false) {
+  const int key = batch * 4 + (with_embed ? 1 : 0) + (penalized ? 2 : 0);
   auto it = e->graphs.find(key);
   if (it != e->graphs.end()) return it->second;
   StepGraph g;
@@ -849,7 +854,7 @@ static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true) {
   cudaGraph_t graph = nullptr;
   CK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
   try {
-    g.launches = enqueue_step(e, batch, g.nsplit, e->stream, with_embed, &g.head_ctas);
+    g.launches = enqueue_step(e, batch, g.nsplit, e->stream, with_embed, &g.head_ctas, penalized);
   } catch (...) {
     cudaStreamEndCapture(e->stream, &graph);
     if (graph) cudaGraphDestroy(graph);

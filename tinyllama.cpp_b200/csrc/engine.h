@@ -80,6 +80,12 @@ struct b200_engine {
   int forced_cap = 0;
   int* d_log = nullptr;
   int log_cap = 0;
+  // repetition penalty of the device-resident greedy loop: window ring, running count, occurrence counts, value
+  int* d_pen_ring = nullptr;
+  int* d_pen_count = nullptr;
+  uint8_t* d_pen_counts = nullptr;  // [max_seqs][pen_stride]: occurrences of each vocabulary index in the window
+  float* d_pen_value = nullptr;
+  int pen_stride = 0;
   float* d_h = nullptr;
   float* d_q = nullptr;
   float* d_kvnew = nullptr;

@@ -167,6 +167,12 @@ struct GemvParams {
   uint2* amax_peer[8];  // tensor parallel: where each rank receives this rank's argmax partials as packets
                         // {value, index | (exchange number & 0x7fff) << 17}, [batch][gridDim.x] each; nullptr: not sent
   unsigned amax_epoch_k; // number of that exchange within the step (added to *epoch_base)
+  // repetition penalty on the logits (reference apply_repetition_penalty, api.cpp:86-97): a row is penalised once per
+  // occurrence of its vocabulary index in the window of generated ids, l -> l / penalty when positive, l * penalty
+  // otherwise; pen_counts [batch][pen_stride] holds the occurrence counts (index = global vocabulary index)
+  const uint8_t* pen_counts;
+  int pen_stride;
+  const float* pen_value;
   const float* resid;   // RESID: y = resid + W x (nullptr: y itself)
   int ntiles;           // over all segments
   int* error_flag;      // set when a bounded wait gives up
@@ -749,8 +755,16 @@ __device__ __forceinline__ void gemv_flush(const GemvParams& prm, GemvShared* sh
                                 : prm.y2 + (size_t)bidx * prm.y2_stride + (seg == 2 ? prm.seg[1].rows : 0) + row;
           *dst = v;
         } else {
-          prm.y[(size_t)bidx * prm.y_stride + row] = tot;
           const int grow = row + prm.amax_row_offset;
+          if (prm.pen_counts) {
+            const int times = prm.pen_counts[(size_t)bidx * prm.pen_stride + grow];
+            if (times) {
+              const float pen = *prm.pen_value;
+#pragma unroll 1
+              for (int k = 0; k < times; ++k) tot = tot > 0.0f ? __fdiv_rn(tot, pen) : __fmul_rn(tot, pen);
+            }
+          }
+          prm.y[(size_t)bidx * prm.y_stride + row] = tot;
           if (tot > best_v || (tot == best_v && grow < best_i)) { best_v = tot; best_i = grow; }
         }
       }

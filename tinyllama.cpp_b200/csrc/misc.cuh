@@ -19,6 +19,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const float* __rest
 // lm_head kernel left, then bookkeeping for the next step: tokens[b] <- chosen (or the forced
 // token while a prompt is being replayed), positions[b] += 1, and the id is appended to the
 // step log. One block; warp w handles sequences w, w+nwarps, ...
+constexpr int PEN_WINDOW = 64;  // reference apply_repetition_penalty: window = 64 generated tokens
+
 struct SelectParams {
   const float* amax_val;  // [ranks][batch][parts_per_rank]
   const int* amax_idx;
@@ -40,6 +42,12 @@ struct SelectParams {
   const uint2* amax_pkts;
   unsigned epoch_k;       // this exchange's number = *epoch + epoch_k
   int* error_flag;
+  // repetition penalty: the window of the last PEN_WINDOW generated ids of every sequence (a ring and its running
+  // count) and the per-id occurrence counts the lm_head launch reads; nullptr: no penalty bookkeeping
+  int* pen_ring;          // [batch][PEN_WINDOW]
+  int* pen_count;         // [batch]
+  uint8_t* pen_counts;    // [batch][pen_stride]
+  int pen_stride;
 };
 
 __global__ void select_kernel(const SelectParams p) {
@@ -81,6 +89,20 @@ __global__ void select_kernel(const SelectParams p) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (p.pen_ring && lane == 0) {
+      // the chosen id enters the window of generated tokens, the id generated PEN_WINDOW steps ago leaves it
+      int* ring = p.pen_ring + (size_t)b * PEN_WINDOW;
+      uint8_t* counts = p.pen_counts + (size_t)b * p.pen_stride;
+      const int cnt = p.pen_count[b];
+      const int at = cnt % PEN_WINDOW;
+      if (cnt >= PEN_WINDOW) {
+        const int old = ring[at];
+        if (old >= 0) counts[old] -= 1;
+      }
+      ring[at] = bi;
+      counts[bi] += 1;
+      p.pen_count[b] = cnt + 1;
     }
     if (lane == 0) {
       p.argmax_out[b] = bi;
