@@ -96,6 +96,10 @@ int b200_prefill(b200_engine* e, int seq_slot, const int32_t* token_ids, int n, 
  * per-token arithmetic as one b200_prefill call per sequence on the tensor-core path (n >= 16). */
 int b200_prefill_batch(b200_engine* e, int n_seqs, const int32_t* slots, const int32_t* token_ids, const int32_t* lens,
                        const int32_t* start_pos, float* host_logits_last);
+/* The chunk plan b200_prefill_batch follows for prompts of these lengths (host arithmetic only, no GPU needed): one
+ * record per run of tokens, out[i] = {chunk, first row in the chunk, tokens, position of the first token, index of the
+ * sequence whose prompt ends with this run or -1}. chunk = tokens per chunk (the engine uses 512). */
+int b200_prefill_plan(int n_seqs, const int32_t* lens, int chunk, int32_t* out /* [max_runs][5] */, int max_runs, int* n_runs);
 
 /* One decode step for `batch` independent sequences: forward_device_batch_generation
  * (model.cpp:1863) with the embedding lookup of the session loop (api.cpp:727) folded in.

@@ -54,3 +54,29 @@ def test_quantised_embedding_table_option(pkg, tmp_path):
         assert np.array_equal(out, table[77])
     plain = pkg.synth.write_gguf(str(tmp_path / "p.gguf"), "tiny", scheme=1)
     assert pkg.gguf.GGUF(plain).tensors["token_embd.weight"]["type"] == 0
+
+
+def test_prefill_chunk_plan(pkg):
+    """Sequence-aware ingestion lays the prompts end to end and cuts every 512 tokens: every token appears exactly once,
+    runs of a sequence are contiguous in position, a chunk never exceeds its size, and each prompt ends exactly one run."""
+    rng = np.random.default_rng(1)
+    for lens, chunk in ([[120, 17, 100, 127, 64, 99, 111, 125, 97], 512], [[512], 512], [[513, 1, 510], 512],
+                        [list(rng.integers(1, 4097, 64)), 512], [[5, 5, 5], 4]):
+        plan = pkg.api.prefill_plan(lens, chunk)
+        per_chunk = {}
+        for c, row0, n, start, ends in plan:
+            assert n >= 1 and row0 == per_chunk.get(c, 0)      # runs tile each chunk without gaps
+            per_chunk[c] = row0 + n
+        assert all(v <= chunk for v in per_chunk.values())
+        assert sorted(per_chunk) == list(range(len(per_chunk)))
+        assert all(per_chunk[c] == chunk for c in list(per_chunk)[:-1])  # every chunk but the last is full
+        seq, pos = 0, 0
+        for c, row0, n, start, ends in plan:                       # runs follow the sequences in order
+            assert start == pos
+            pos += n
+            if pos == lens[seq]:
+                assert ends == seq
+                seq, pos = seq + 1, 0
+            else:
+                assert ends == -1
+        assert seq == len(lens) and pos == 0

@@ -28,7 +28,7 @@ class ModelDesc(ctypes.Structure):
 EXPORTS = [
     "b200_last_error", "b200_device_count", "b200_engine_create", "b200_engine_upload_tensor",
     "b200_engine_finalize", "b200_engine_load_gguf", "b200_engine_get_desc", "b200_engine_destroy",
-    "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_prefill_batch", "b200_decode",
+    "b200_kv_reset", "b200_lookup_embedding", "b200_forward", "b200_prefill", "b200_prefill_batch", "b200_prefill_plan", "b200_decode",
     "b200_generate_greedy", "b200_generate_greedy_penalized", "b200_dequant", "b200_matvec", "b200_matmul", "b200_rmsnorm", "b200_rmsnorm_batch",
     "b200_fused_qkv_rope", "b200_fused_gate_up_swiglu", "b200_attention_decode", "b200_attention_prefill",
     "b200_attention_decode_noalloc", "b200_engine_stats", "b200_engine_time_kernel", "b200_engine_read_trace",
@@ -61,6 +61,7 @@ def lib():
     L.b200_prefill.argtypes = [_vp, _i, _vp, _i, _i, _vp]
     L.b200_decode.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
     L.b200_prefill_batch.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp]
+    L.b200_prefill_plan.argtypes = [_i, _vp, _i, _vp, _i, ctypes.POINTER(_i)]
     L.b200_generate_greedy.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _vp, ctypes.POINTER(ctypes.c_float)]
     L.b200_generate_greedy_penalized.argtypes = [_vp, _i, _vp, _vp, _vp, _i, ctypes.c_float, _vp, _vp, _vp, ctypes.POINTER(ctypes.c_float)]
     L.b200_dequant.argtypes = [_i, _vp, _sz, _vp]
@@ -236,6 +237,16 @@ class Engine:
         us, nbytes = ctypes.c_float(0), _i64(0)
         _check(lib().b200_engine_time_kernel(self._h, which, iters, ctypes.byref(us), ctypes.byref(nbytes)))
         return us.value, nbytes.value
+
+
+def prefill_plan(lens, chunk=512):
+    """Runs of the sequence-aware chunk plan: rows of (chunk, row0, tokens, first position, ending sequence or -1)."""
+    lens = _i32(lens)
+    cap = int(lens.sum() // chunk + 2 * len(lens) + 2)
+    out = np.zeros((cap, 5), np.int32)
+    n = _i(0)
+    _check(lib().b200_prefill_plan(len(lens), _ptr(lens), chunk, _ptr(out), cap, ctypes.byref(n)))
+    return out[:n.value].copy()
 
 
 def dequant(ggml_type, blocks, n_blocks):

@@ -815,35 +815,59 @@ static void prefill_chunk(b200_engine* e, int T, const std::vector<int>& meta, c
 // Prompt ingestion of one or several sequences through the tensor-core path: the tokens of all sequences are laid
 // end to end and cut into chunks of PF_CHUNK, so that short prompts share a chunk (and its weight traffic).
 // host_logits: [n_seqs][V] or nullptr.
-static void prefill_sequences(b200_engine* e, int n_seqs, const int32_t* slots, const int32_t* ids, const int32_t* lens, const int32_t* start_pos,
-                              float* host_logits) {
-  std::vector<int> meta;
-  std::vector<PrefillRun> runs;
-  auto flush = [&](int T) {
-    // meta holds [id, pos, slot] triples of T tokens: regroup into the three arrays the kernels read
-    std::vector<int> m((size_t)3 * T);
-    for (int t = 0; t < T; ++t) { m[t] = meta[3 * t]; m[T + t] = meta[3 * t + 1]; m[2 * T + t] = meta[3 * t + 2]; }
-    prefill_chunk(e, T, m, runs, host_logits);
-    meta.clear();
-    runs.clear();
-  };
-  int T = 0;
-  size_t off = 0;
+// The chunk plan of a sequence-aware ingestion: the prompts laid end to end and cut every `chunk` tokens. Each run is
+// a stretch of one sequence inside one chunk; runs are returned in order, `chunk_of[i]` = the chunk run i belongs to.
+// Pure host arithmetic (exposed through b200_prefill_plan so that it can be checked without a GPU).
+static void plan_prefill_runs(int n_seqs, const int32_t* slots, const int32_t* lens, const int32_t* start_pos, int chunk,
+                              std::vector<PrefillRun>& runs, std::vector<int>& chunk_of) {
+  int T = 0, c = 0;
   for (int s = 0; s < n_seqs; ++s) {
     int done = 0;
     while (done < lens[s]) {
-      const int take = std::min(lens[s] - done, PF_CHUNK - T);
-      runs.push_back({T, take, slots[s], start_pos[s] + done, done + take == lens[s] ? s : -1});
-      for (int t = 0; t < take; ++t) { meta.push_back(ids[off + done + t]); meta.push_back(start_pos[s] + done + t); meta.push_back(slots[s]); }
+      const int take = std::min(lens[s] - done, chunk - T);
+      runs.push_back({T, take, slots ? slots[s] : s, (start_pos ? start_pos[s] : 0) + done, done + take == lens[s] ? s : -1});
+      chunk_of.push_back(c);
       T += take;
       done += take;
-      if (T == PF_CHUNK) { flush(T); T = 0; }
+      if (T == chunk) { T = 0; ++c; }
     }
-    off += (size_t)lens[s];
   }
-  if (T > 0) flush(T);
 }
 
+static void prefill_sequences(b200_engine* e, int n_seqs, const int32_t* slots, const int32_t* ids, const int32_t* lens, const int32_t* start_pos,
+                              float* host_logits) {
+  std::vector<PrefillRun> all;
+  std::vector<int> chunk_of;
+  plan_prefill_runs(n_seqs, slots, lens, start_pos, PF_CHUNK, all, chunk_of);
+  std::vector<size_t> seq_off(n_seqs + 1, 0);
+  for (int s = 0; s < n_seqs; ++s) seq_off[s + 1] = seq_off[s] + (size_t)lens[s];
+  // which sequence a run belongs to: runs come in sequence order, a new sequence starts when the previous one's last run ended
+  size_t i = 0;
+  int seq = 0, done = 0;
+  while (i < all.size()) {
+    const int c = chunk_of[i];
+    std::vector<PrefillRun> runs;
+    std::vector<int> tok, pos, slot;
+    for (; i < all.size() && chunk_of[i] == c; ++i) {
+      const PrefillRun& r = all[i];
+      runs.push_back(r);
+      for (int t = 0; t < r.len; ++t) {
+        tok.push_back(ids[seq_off[seq] + done + t]);
+        pos.push_back(r.start + t);
+        slot.push_back(r.slot);
+      }
+      done += r.len;
+      if (done == lens[seq]) { ++seq; done = 0; }
+    }
+    const int T = (int)tok.size();
+    std::vector<int> meta;
+    meta.reserve((size_t)3 * T);
+    meta.insert(meta.end(), tok.begin(), tok.end());
+    meta.insert(meta.end(), pos.begin(), pos.end());
+    meta.insert(meta.end(), slot.begin(), slot.end());
+    prefill_chunk(e, T, meta, runs, host_logits);
+  }
+}
 
 static StepGraph& get_graph(b200_engine* e, int batch, bool with_embed = true, bool penalized = false) {
   const int key = batch * 4 + (with_embed ? 1 : 0) + (penalized ? 2 : 0);
